@@ -1,0 +1,167 @@
+// C ABI of libintfa.so: argument validation, error reporting, dispatch.
+// Nothing here throws or aborts; every entry point returns a status code.
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "intfa_internal.h"
+
+namespace intfa {
+
+static thread_local char g_err[512] = "";
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int sm_count_cached() {
+  static int cache[64];
+  static bool have[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (!have[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+    cache[dev] = n;
+    have[dev] = true;
+  }
+  return cache[dev];
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int check_tma_tensor(const char* name, const void* ptr, const int64_t* st, int esize) {
+  if (!ptr) return set_error(INTFA_ERR_INVALID_ARG, "%s is NULL", name);
+  if (!aligned16(ptr)) return set_error(INTFA_ERR_INVALID_ARG, "%s must be 16-byte aligned", name);
+  for (int i = 0; i < 3; ++i)
+    if (st[i] <= 0 || (st[i] * esize) % 16 != 0)
+      return set_error(INTFA_ERR_INVALID_ARG, "%s stride[%d]=%lld: byte strides must be positive multiples of 16", name,
+                       i, (long long)st[i]);
+  return INTFA_OK;
+}
+
+}  // namespace intfa
+
+using namespace intfa;
+
+extern "C" {
+
+int intfa_version(void) { return 100; }
+
+int intfa_last_error(char* buf, size_t len) {
+  if (!buf || len == 0) return INTFA_ERR_INVALID_ARG;
+  strncpy(buf, g_err, len - 1);
+  buf[len - 1] = 0;
+  return INTFA_OK;
+}
+
+int intfa_sm_count(void) { return sm_count_cached(); }
+
+int intfa_fwd(const IntfaFwdParams* p, void* stream) {
+  if (!p) return set_error(INTFA_ERR_INVALID_ARG, "params is NULL");
+  if (p->variant != INTFA_VARIANT_FULL && p->variant != INTFA_VARIANT_HALF)
+    return set_error(INTFA_ERR_INVALID_ARG, "variant must be INTFA_VARIANT_FULL or INTFA_VARIANT_HALF");
+  const bool full = p->variant == INTFA_VARIANT_FULL;
+  if (p->B <= 0 || p->H <= 0 || p->Nq <= 0 || p->Nk <= 0)
+    return set_error(INTFA_ERR_INVALID_ARG, "B, H, Nq, Nk must be positive");
+  if (p->D != 64 && p->D != 128)
+    return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: the sm_100a kernels cover 64 and 128", p->D);
+  if (p->G != 64 && p->G != 128) return set_error(INTFA_ERR_UNSUPPORTED, "G=%d unsupported: 64 or 128", p->G);
+  if (p->G > p->D)
+    return set_error(INTFA_ERR_UNSUPPORTED, "G=%d > head_dim=%d unsupported (the reference requires BLOCK_N <= HEAD_DIM)",
+                     p->G, p->D);
+  if (p->Nq % 128 != 0) return set_error(INTFA_ERR_UNSUPPORTED, "Nq=%d must be a multiple of 128", p->Nq);
+  if (p->Nk % p->G != 0) return set_error(INTFA_ERR_UNSUPPORTED, "Nk=%d must be a multiple of G=%d", p->Nk, p->G);
+  if (p->p_round != 0 && p->p_round != 1) return set_error(INTFA_ERR_INVALID_ARG, "p_round must be 0 or 1");
+  if ((long long)p->B * p->H * (p->Nq / 128) > 0x7fffffffLL) return set_error(INTFA_ERR_TOO_LARGE, "too many work items");
+  int rc;
+  if ((rc = check_tma_tensor("q", p->q, p->q_stride, 1))) return rc;
+  if ((rc = check_tma_tensor("k", p->k, p->k_stride, 1))) return rc;
+  if ((rc = check_tma_tensor("v", p->v, p->v_stride, full ? 1 : 2))) return rc;
+  if (!p->q_scale || !p->k_scale) return set_error(INTFA_ERR_INVALID_ARG, "q_scale / k_scale is NULL");
+  if (!aligned16(p->k_scale) || p->ks_stride[0] % 4 != 0 || p->ks_stride[1] % 4 != 0)
+    return set_error(INTFA_ERR_INVALID_ARG, "k_scale must be 16-byte aligned with (B,H) strides that are multiples of 4");
+  if (full && !p->v_scale) return set_error(INTFA_ERR_INVALID_ARG, "v_scale is NULL (full-int8)");
+  if (p->write_o) {
+    if (!p->o) return set_error(INTFA_ERR_INVALID_ARG, "o is NULL");
+    if (!aligned16(p->o) || p->o_stride[0] % 8 || p->o_stride[1] % 8 || p->o_stride[2] % 8)
+      return set_error(INTFA_ERR_INVALID_ARG, "o must be 16-byte aligned with strides that are multiples of 8 elements");
+  }
+  if ((p->state_in || p->state_out) && (!p->state_m || !p->state_l || !p->state_acc))
+    return set_error(INTFA_ERR_INVALID_ARG, "state_in/state_out set but a state pointer is NULL");
+  if ((p->state_in || p->state_out) && !aligned16(p->state_acc))
+    return set_error(INTFA_ERR_INVALID_ARG, "state_acc must be 16-byte aligned");
+  if (!p->write_o && !p->state_out) return set_error(INTFA_ERR_INVALID_ARG, "nothing to write: write_o and state_out are both 0");
+  if (p->dbg_s && (p->dbg_tile < 0 || p->dbg_step < 0)) return set_error(INTFA_ERR_INVALID_ARG, "bad debug tap");
+  return fwd_dispatch(p, reinterpret_cast<cudaStream_t>(stream));
+}
+
+static int check_quant_args(const void* x, const int64_t* st, const void* x8, const float* scale, int B, int H, int N,
+                            int D) {
+  if (!x || !st || !x8 || !scale) return set_error(INTFA_ERR_INVALID_ARG, "NULL argument");
+  if (B <= 0 || H <= 0 || N <= 0) return set_error(INTFA_ERR_INVALID_ARG, "B, H, N must be positive");
+  if (D != 64 && D != 128) return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: 64 or 128", D);
+  if (!aligned16(x) || st[0] % 8 || st[1] % 8 || st[2] % 8)
+    return set_error(INTFA_ERR_INVALID_ARG, "input rows must be 16-byte aligned (pointer and strides multiples of 8 elements)");
+  if (!aligned16(x8)) return set_error(INTFA_ERR_INVALID_ARG, "int8 output must be 16-byte aligned");
+  return INTFA_OK;
+}
+
+int intfa_quant_pertoken(const void* x, const int64_t x_stride[3], void* x8, float* scale, int32_t B, int32_t H,
+                         int32_t N, int32_t D, void* stream) {
+  int rc = check_quant_args(x, x_stride, x8, scale, B, H, N, D);
+  if (rc) return rc;
+  return quant_pertoken(x, x_stride, x8, scale, B, H, N, D, reinterpret_cast<cudaStream_t>(stream));
+}
+
+size_t intfa_quant_v_workspace_bytes(int32_t B, int32_t H, int32_t D) {
+  if (B <= 0 || H <= 0 || D <= 0) return 0;
+  return (size_t)B * H * D * sizeof(unsigned int);
+}
+
+int intfa_quant_v(const void* v, const int64_t v_stride[3], void* v8, float* scale, int32_t mode, int32_t B, int32_t H,
+                  int32_t N, int32_t D, void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_quant_args(v, v_stride, v8, scale, B, H, N, D);
+  if (rc) return rc;
+  if (mode != INTFA_VSCALE_PER_TENSOR && mode != INTFA_VSCALE_PER_CHANNEL)
+    return set_error(INTFA_ERR_INVALID_ARG, "mode must be INTFA_VSCALE_PER_TENSOR or INTFA_VSCALE_PER_CHANNEL");
+  if (!workspace || workspace_bytes < intfa_quant_v_workspace_bytes(B, H, D))
+    return set_error(INTFA_ERR_INVALID_ARG, "workspace missing or smaller than intfa_quant_v_workspace_bytes()");
+  if ((long long)B * H > 65535) return set_error(INTFA_ERR_TOO_LARGE, "B*H=%lld exceeds 65535", (long long)B * H);
+  return quant_v(v, v_stride, v8, scale, mode, B, H, N, D, workspace, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int intfa_v_colmax(const void* v, const int64_t v_stride[3], void* colmax, int32_t B, int32_t H, int32_t N, int32_t D,
+                   void* stream) {
+  if (!v || !v_stride || !colmax) return set_error(INTFA_ERR_INVALID_ARG, "NULL argument");
+  if (B <= 0 || H <= 0 || N <= 0) return set_error(INTFA_ERR_INVALID_ARG, "B, H, N must be positive");
+  if (D != 64 && D != 128) return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: 64 or 128", D);
+  if (!aligned16(v) || v_stride[0] % 8 || v_stride[1] % 8 || v_stride[2] % 8)
+    return set_error(INTFA_ERR_INVALID_ARG, "input rows must be 16-byte aligned (pointer and strides multiples of 8 elements)");
+  if ((long long)B * H > 65535) return set_error(INTFA_ERR_TOO_LARGE, "B*H=%lld exceeds 65535", (long long)B * H);
+  return v_colmax(v, v_stride, colmax, B, H, N, D, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int intfa_v_quant_from_colmax(const void* v, const int64_t v_stride[3], const void* colmax, void* v8, float* scale,
+                              int32_t mode, int32_t B, int32_t H, int32_t N, int32_t D, void* stream) {
+  int rc = check_quant_args(v, v_stride, v8, scale, B, H, N, D);
+  if (rc) return rc;
+  if (!colmax) return set_error(INTFA_ERR_INVALID_ARG, "colmax is NULL");
+  if (mode != INTFA_VSCALE_PER_TENSOR && mode != INTFA_VSCALE_PER_CHANNEL)
+    return set_error(INTFA_ERR_INVALID_ARG, "mode must be INTFA_VSCALE_PER_TENSOR or INTFA_VSCALE_PER_CHANNEL");
+  if ((long long)B * H > 65535) return set_error(INTFA_ERR_TOO_LARGE, "B*H=%lld exceeds 65535", (long long)B * H);
+  return v_quant_from_colmax(v, v_stride, colmax, v8, scale, mode, B, H, N, D, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int intfa_scales_f16_to_f32(const void* src_f16, float* dst_f32, int64_t n, void* stream) {
+  if (n < 0 || (n > 0 && (!src_f16 || !dst_f32))) return set_error(INTFA_ERR_INVALID_ARG, "bad argument");
+  return scales_f16_to_f32(src_f16, dst_f32, n, reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

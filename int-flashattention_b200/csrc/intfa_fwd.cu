@@ -1,0 +1,622 @@
+// INT8 FlashAttention forward for sm_100a.
+//
+// One CTA owns one 128-row query tile at a time (persistent over a static list of
+// (batch*head, query-block) work items) and walks the KV sequence ASCENDING in tiles
+// of G columns -- G is also the granularity at which the running row maximum is
+// updated, which the full-int8 result depends on (the reference's BLOCK_N,
+// flash_atten_full_int8.py:30-70).
+//
+// Warp roles (256 threads):
+//   warp 0      TMA producer: Q tile once per work item; K tile, V tile and the K-scale
+//               slice through an NS-stage shared-memory ring (cp.async.bulk.tensor, no multicast)
+//   warp 1      MMA issuer (one thread): S = Q K^T  with tcgen05.mma kind::i8 into an int32
+//               TMEM accumulator; O_j = P V with kind::i8 (full) or kind::f16 (half)
+//   warp 2      TMEM allocator
+//   warps 4-7   softmax/correction/epilogue, one thread per query row: TMEM -> registers,
+//               dequantise with s_q[row]*s_k[col], online softmax, P -> int8 (or fp16) into
+//               swizzled shared memory for the second MMA, then acc = acc*alpha + O_j*s_v/127
+//               in fp32 registers (the int32 PV tile cannot absorb the fp32 rescale, so PV
+//               never accumulates across KV tiles in TMEM).
+//
+// Arithmetic contract (what the parity tests pin; reference lines in parentheses):
+//   s   = (fp32(S32) * s_q[row]) * s_k[col]                 (flash_atten_full_int8.py:36-38)
+//   m'  = max(m, rowmax(s) * c),  x = s*c - m'   (fma)      (:45-46)   c = sm_scale*1.44269504 (:157)
+//   on the causal diagonal band:  x0 = s*c + (col<=row ? 0 : -1e6), m' = max(m,rowmax(x0)) (:40-43)
+//   p   = exp2(x), l_j = sum p (unquantised), alpha = exp2(m - m')     (:47-48,53-54)
+//   full: p8 = trunc(fp16(fp16(fp16(p)*127) + 0.5))          (:49-51)
+//         acc = acc*alpha + fp32(P8 V8) * (s_v[ch]/127)      (:56-62)
+//   half: acc = acc*alpha + fp16(p) V16 (fp32 accumulate)    (flash_atten_int8.py:54-59)
+//   m carried across the off-band/on-band boundary           (flash_atten_int8.py:66,157,166)
+//   o   = fp16(acc / l)                                      (:181-182)
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "intfa_internal.h"
+#include "intfa_ptx.cuh"
+
+namespace intfa {
+
+constexpr int kBM = 128;          // query rows per work item
+constexpr int kThreads = 256;
+constexpr int kComputeThreads = 128;
+
+// device-side wait codes stored in *status (low byte = which wait, bits 8.. = blockIdx)
+enum WaitCode {
+  W_Q_EMPTY = 1, W_K_EMPTY, W_V_EMPTY, W_Q_FULL, W_K_FULL, W_V_FULL, W_P_FULL, W_O_EMPTY,
+  W_S_FULL, W_O_FULL, W_KS_FULL
+};
+
+template <int D, int G, bool FULL>
+struct Cfg {
+  static constexpr int Q_BYTES = kBM * D;
+  static constexpr int K_BYTES = G * D;
+  static constexpr int V_BYTES = FULL ? G * D : G * D * 2;
+  static constexpr int P_BYTES = FULL ? kBM * G : kBM * G * 2;
+  static constexpr int KS_BYTES = G * 4;
+  // stages: keep the CTA under ~104 KB so two CTAs share an SM where possible
+  static constexpr int BUDGET = 104 * 1024;
+  static constexpr int FIXED = Q_BYTES + P_BYTES + 2048;
+  static constexpr int PER_STAGE = K_BYTES + V_BYTES + KS_BYTES;
+  static constexpr int NS_RAW = (BUDGET - FIXED) / PER_STAGE;
+  static constexpr int NS = NS_RAW < 2 ? 2 : (NS_RAW > 4 ? 4 : NS_RAW);
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + Q_BYTES;
+  static constexpr int OFF_V = OFF_K + NS * K_BYTES;
+  static constexpr int OFF_P = OFF_V + NS * V_BYTES;
+  static constexpr int OFF_KS = OFF_P + P_BYTES;
+  static constexpr int OFF_VSD = OFF_KS + NS * KS_BYTES;
+  static constexpr int OFF_BAR = OFF_VSD + D * 4;
+  static constexpr int NUM_BARS = 6 + 4 * NS;
+  static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
+  static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;   // +1024: manual alignment slack
+  static constexpr int TMEM_COLS = (G + D) <= 128 ? 128 : 256;
+  static constexpr int COL_S = 0;
+  static constexpr int COL_O = (G + D) <= 128 ? 64 : 128;
+  // swizzle span = bytes of one operand row
+  static constexpr uint64_t SWZ_QK = (D == 128) ? kSwz128 : kSwz64;     // Q, K rows are D bytes
+  static constexpr uint32_t SBO_QK = 8 * D;
+  static constexpr uint64_t SWZ_P = FULL ? ((G == 128) ? kSwz128 : kSwz64) : kSwz128;
+  static constexpr uint32_t SBO_P = FULL ? 8 * G : 1024;
+  static constexpr uint64_t SWZ_V = FULL ? ((D == 128) ? kSwz128 : kSwz64) : kSwz128;
+  static constexpr uint32_t SBO_V = FULL ? 8 * D : 1024;
+  static constexpr uint32_t IDESC_QK = make_idesc(2, 1, 1, 0, 0, kBM, G);
+  static constexpr uint32_t IDESC_PV = FULL ? make_idesc(2, 1, 1, 0, 1, kBM, D) : make_idesc(1, 0, 0, 0, 1, kBM, D);
+};
+
+struct TileInfo {
+  int bh, b, h, mb, work, nsteps;
+};
+
+__device__ __forceinline__ TileInfo decode_tile(const KParams& p, int tile, int G) {
+  TileInfo t;
+  t.bh = tile / p.MB;
+  const int i = tile - t.bh * p.MB;
+  t.mb = p.causal ? (p.MB - 1 - i) : i;       // causal: long rows first
+  t.b = t.bh / p.H;
+  t.h = t.bh - t.b * p.H;
+  t.work = t.bh * p.MB + t.mb;
+  int n = p.Nk / G;
+  if (p.causal) {
+    // last visible global column for the last row of the block
+    const long long last_row = p.q_off + (long long)t.mb * kBM + (kBM - 1);
+    const long long rel = last_row - p.kv_off;           // last visible local column
+    long long nv = rel < 0 ? 0 : (rel / G + 1);
+    if (nv < n) n = (int)nv;
+  }
+  t.nsteps = n;
+  return t;
+}
+
+// byte offset of 16-byte chunk `chunk` of row `row` inside a swizzled [rows][ROWB bytes] tile
+template <int ROWB>
+__device__ __forceinline__ uint32_t swz_off(int row, int chunk) {
+  constexpr int MASK = ROWB / 16 - 1;     // 7 for 128-byte rows, 3 for 64-byte rows
+  const uint32_t a = row * ROWB + chunk * 16;
+  return a ^ (((a >> 7) & MASK) << 4);
+}
+
+template <int D, int G, bool FULL, bool PRNE>
+__global__ void __launch_bounds__(kThreads, 2)
+intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const KParams p) {
+  using C = Cfg<D, G, FULL>;
+  constexpr int NS = C::NS;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  const uint32_t bar0 = smem_u32(bars);
+  auto BAR = [&](int i) { return bar0 + 8u * i; };
+  // barrier indices
+  constexpr int B_QFULL = 0, B_QEMPTY = 1, B_SFULL = 2, B_PFULL = 3, B_OFULL = 4, B_OEMPTY = 5;
+  constexpr int B_KFULL = 6, B_KEMPTY = 6 + NS, B_VFULL = 6 + 2 * NS, B_VEMPTY = 6 + 3 * NS;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 4);
+
+  if (threadIdx.x == 0) {
+    mbar_init(BAR(B_QFULL), 1);
+    mbar_init(BAR(B_QEMPTY), 1);
+    mbar_init(BAR(B_SFULL), 1);
+    mbar_init(BAR(B_PFULL), 4);
+    mbar_init(BAR(B_OFULL), 1);
+    mbar_init(BAR(B_OEMPTY), 4);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(BAR(B_KFULL + s), 1);
+      mbar_init(BAR(B_KEMPTY + s), 1);
+      mbar_init(BAR(B_VFULL + s), 1);
+      mbar_init(BAR(B_VEMPTY + s), 1);
+    }
+    *abort_flag = 0;
+    mbar_init_fence();
+    fence_proxy_async_smem();
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base + C::COL_S;
+  const uint32_t tO = tmem_base + C::COL_O;
+  const int code_hi = (int)(blockIdx.x << 8);
+
+  const uint32_t sQ = smem_u32(smem + C::OFF_Q);
+  const uint32_t sK = smem_u32(smem + C::OFF_K);
+  const uint32_t sV = smem_u32(smem + C::OFF_V);
+  const uint32_t sP = smem_u32(smem + C::OFF_P);
+  const uint32_t sKS = smem_u32(smem + C::OFF_KS);
+
+  if (warp < 4) {
+    reg_dealloc<40>();
+    if (warp == 0 && lane == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      prefetch_tmap(&tmQ);
+      prefetch_tmap(&tmK);
+      prefetch_tmap(&tmV);
+      uint32_t kv_it = 0, tile_it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        const TileInfo t = decode_tile(p, tile, G);
+        if (t.nsteps == 0) continue;
+        ok = mbar_wait(BAR(B_QEMPTY), (tile_it & 1) ^ 1, abort_flag, p.status, code_hi | W_Q_EMPTY);
+        if (!ok) break;
+        mbar_expect_tx(BAR(B_QFULL), C::Q_BYTES);
+        tma_load_4d(sQ, &tmQ, BAR(B_QFULL), 0, t.mb * kBM, t.h, t.b);
+        const float* ks_row = p.ks + (long long)t.b * p.ks_sb + (long long)t.h * p.ks_sh;
+        for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
+          const uint32_t s = kv_it % NS, ph = (kv_it / NS) & 1;
+          ok = mbar_wait(BAR(B_KEMPTY + s), ph ^ 1, abort_flag, p.status, code_hi | W_K_EMPTY);
+          if (!ok) break;
+          mbar_expect_tx(BAR(B_KFULL + s), C::K_BYTES);
+          tma_load_4d(sK + s * C::K_BYTES, &tmK, BAR(B_KFULL + s), 0, j * G, t.h, t.b);
+          ok = mbar_wait(BAR(B_VEMPTY + s), ph ^ 1, abort_flag, p.status, code_hi | W_V_EMPTY);
+          if (!ok) break;
+          mbar_expect_tx(BAR(B_VFULL + s), C::V_BYTES + C::KS_BYTES);
+          if constexpr (FULL) {
+            tma_load_4d(sV + s * C::V_BYTES, &tmV, BAR(B_VFULL + s), 0, j * G, t.h, t.b);
+          } else {
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c)
+              tma_load_4d(sV + s * C::V_BYTES + c * (G * 128), &tmV, BAR(B_VFULL + s), c * 64, j * G, t.h, t.b);
+          }
+          bulk_load_1d(sKS + s * C::KS_BYTES, ks_row + j * G, C::KS_BYTES, BAR(B_VFULL + s));
+        }
+        ++tile_it;
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ------------------------------------------------------------------ MMA issuer
+      uint32_t kv_it = 0;      // KV tiles whose QK has been issued
+      uint32_t step_it = 0;    // KV tiles whose PV has been issued
+      uint32_t tile_it = 0;
+      bool ok = true;
+      auto issue_qk = [&](uint32_t it) -> bool {
+        const uint32_t s = it % NS, ph = (it / NS) & 1;
+        if (!mbar_wait(BAR(B_KFULL + s), ph, abort_flag, p.status, code_hi | W_K_FULL)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 32; ++kk) {
+          const uint64_t ad = make_smem_desc(sQ + kk * 32, 16, C::SBO_QK, C::SWZ_QK);
+          const uint64_t bd = make_smem_desc(sK + s * C::K_BYTES + kk * 32, 16, C::SBO_QK, C::SWZ_QK);
+          umma_i8(tS, ad, bd, C::IDESC_QK, kk > 0);
+        }
+        umma_commit(BAR(B_SFULL));
+        umma_commit(BAR(B_KEMPTY + s));
+        return true;
+      };
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        const TileInfo t = decode_tile(p, tile, G);
+        if (t.nsteps == 0) continue;
+        ok = mbar_wait(BAR(B_QFULL), tile_it & 1, abort_flag, p.status, code_hi | W_Q_FULL);
+        if (!ok) break;
+        ok = issue_qk(kv_it++);
+        if (!ok) break;
+        if (t.nsteps == 1) umma_commit(BAR(B_QEMPTY));
+        for (int j = 0; j < t.nsteps; ++j, ++step_it) {
+          const uint32_t s = step_it % NS, ph = (step_it / NS) & 1;
+          ok = mbar_wait(BAR(B_PFULL), step_it & 1, abort_flag, p.status, code_hi | W_P_FULL);
+          if (!ok) break;
+          ok = mbar_wait(BAR(B_VFULL + s), ph, abort_flag, p.status, code_hi | W_V_FULL);
+          if (!ok) break;
+          ok = mbar_wait(BAR(B_OEMPTY), (step_it & 1) ^ 1, abort_flag, p.status, code_hi | W_O_EMPTY);
+          if (!ok) break;
+          tc_fence_after();
+          if constexpr (FULL) {
+#pragma unroll
+            for (int kk = 0; kk < G / 32; ++kk) {
+              const uint64_t ad = make_smem_desc(sP + kk * 32, 16, C::SBO_P, C::SWZ_P);
+              const uint64_t bd = make_smem_desc(sV + s * C::V_BYTES + kk * (32 * D), 16, C::SBO_V, C::SWZ_V);
+              umma_i8(tO, ad, bd, C::IDESC_PV, kk > 0);
+            }
+          } else {
+#pragma unroll
+            for (int kk = 0; kk < G / 16; ++kk) {
+              const uint64_t ad =
+                  make_smem_desc(sP + (kk >> 2) * (kBM * 128) + (kk & 3) * 32, 16, C::SBO_P, C::SWZ_P);
+              const uint64_t bd = make_smem_desc(sV + s * C::V_BYTES + kk * 2048, G * 128, C::SBO_V, C::SWZ_V);
+              umma_f16(tO, ad, bd, C::IDESC_PV, kk > 0);
+            }
+          }
+          umma_commit(BAR(B_OFULL));
+          umma_commit(BAR(B_VEMPTY + s));
+          if (j + 1 < t.nsteps) {
+            ok = issue_qk(kv_it++);
+            if (!ok) break;
+            if (j + 2 == t.nsteps) umma_commit(BAR(B_QEMPTY));
+          }
+        }
+        ++tile_it;
+      }
+    }
+    __syncwarp();
+  } else {
+    // -------------------------------------------------------------------- softmax / correction / epilogue
+    reg_alloc<216>();
+    const int row = threadIdx.x - 128;                       // row of the query tile == TMEM lane
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    float* vsd_s = reinterpret_cast<float*>(smem + C::OFF_VSD);
+    uint8_t* sP_gen = smem + C::OFF_P;
+    uint32_t step_it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+      const TileInfo t = decode_tile(p, tile, G);
+      const long long rowg = (long long)t.bh * p.Nq + (long long)t.mb * kBM + row;   // row in [B*H*Nq)
+      const long long grow = p.q_off + (long long)t.mb * kBM + row;                  // global position
+      const float qs_r = p.qs[(long long)t.b * p.qs_sb + (long long)t.h * p.qs_sh + t.mb * kBM + row];
+      float m_i = -INFINITY, l_i = 1.0f;
+      float acc[D];
+      if (p.state_in) {
+        m_i = p.st_m[rowg];
+        l_i = p.st_l[rowg];
+        const float4* a4 = reinterpret_cast<const float4*>(p.st_acc + rowg * D);
+#pragma unroll
+        for (int i = 0; i < D / 4; ++i) {
+          const float4 v = a4[i];
+          acc[4 * i] = v.x; acc[4 * i + 1] = v.y; acc[4 * i + 2] = v.z; acc[4 * i + 3] = v.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < D; ++i) acc[i] = 0.f;
+      }
+      if constexpr (FULL) {
+        named_bar_sync(1, kComputeThreads);       // previous work item done with vsd_s
+        if (row < D)
+          vsd_s[row] = p.vs[(long long)t.b * p.vs_sb + (long long)t.h * p.vs_sh + (long long)row * p.vs_sd] / 127.0f;
+        named_bar_sync(1, kComputeThreads);
+      }
+
+      for (int j = 0; ok && j < t.nsteps; ++j, ++step_it) {
+        const uint32_t s = step_it % NS, ph = (step_it / NS) & 1;
+        const float* ks_s = reinterpret_cast<const float*>(smem + C::OFF_KS + s * C::KS_BYTES);
+        ok = mbar_wait(BAR(B_VFULL + s), ph, abort_flag, p.status, code_hi | W_KS_FULL);
+        if (!ok) break;
+        ok = mbar_wait(BAR(B_SFULL), step_it & 1, abort_flag, p.status, code_hi | W_S_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        const long long gcol0 = p.kv_off + (long long)j * G;
+        const bool masked = p.causal && (gcol0 + G - 1 > p.q_off + (long long)t.mb * kBM);
+        const bool dbg_here = (p.dbg_s != nullptr) && t.work == p.dbg_tile && j == p.dbg_step;
+        const float c = p.c;
+
+        // ---- pass 1: row maximum
+        float mx = -INFINITY;
+#pragma unroll
+        for (int cc = 0; cc < G / 32; ++cc) {
+          uint32_t r[32];
+          tmem_ld32(tS + lane_sel + cc * 32, r);
+          tmem_ld_wait(r);
+          if (dbg_here) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) p.dbg_s[row * G + cc * 32 + i] = (int)r[i];
+          }
+          const float4* k4 = reinterpret_cast<const float4*>(ks_s + cc * 32);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 kk = k4[i];
+            float s0 = (__int2float_rn((int)r[4 * i + 0]) * qs_r) * kk.x;
+            float s1 = (__int2float_rn((int)r[4 * i + 1]) * qs_r) * kk.y;
+            float s2 = (__int2float_rn((int)r[4 * i + 2]) * qs_r) * kk.z;
+            float s3 = (__int2float_rn((int)r[4 * i + 3]) * qs_r) * kk.w;
+            if (masked) {
+              const long long gc = gcol0 + cc * 32 + 4 * i;
+              s0 = fmaf(s0, c, (gc + 0 <= grow) ? 0.f : -1.0e6f);
+              s1 = fmaf(s1, c, (gc + 1 <= grow) ? 0.f : -1.0e6f);
+              s2 = fmaf(s2, c, (gc + 2 <= grow) ? 0.f : -1.0e6f);
+              s3 = fmaf(s3, c, (gc + 3 <= grow) ? 0.f : -1.0e6f);
+            }
+            mx = fmaxf(mx, fmaxf(fmaxf(s0, s1), fmaxf(s2, s3)));
+          }
+        }
+        const float m_new = masked ? fmaxf(m_i, mx) : fmaxf(m_i, mx * c);
+        const float alpha = ex2_approx(m_i - m_new);
+
+        // ---- pass 2: p = exp2(x), row sum, P -> shared memory
+        float lsum = 0.f;
+#pragma unroll
+        for (int cc = 0; cc < G / 32; ++cc) {
+          uint32_t r[32];
+          tmem_ld32(tS + lane_sel + cc * 32, r);
+          tmem_ld_wait(r);
+          const float4* k4 = reinterpret_cast<const float4*>(ks_s + cc * 32);
+          uint32_t pk[FULL ? 8 : 16];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 kk = k4[i];
+            float s0 = (__int2float_rn((int)r[4 * i + 0]) * qs_r) * kk.x;
+            float s1 = (__int2float_rn((int)r[4 * i + 1]) * qs_r) * kk.y;
+            float s2 = (__int2float_rn((int)r[4 * i + 2]) * qs_r) * kk.z;
+            float s3 = (__int2float_rn((int)r[4 * i + 3]) * qs_r) * kk.w;
+            float x0, x1, x2, x3;
+            if (masked) {
+              const long long gc = gcol0 + cc * 32 + 4 * i;
+              x0 = fmaf(s0, c, (gc + 0 <= grow) ? 0.f : -1.0e6f) - m_new;
+              x1 = fmaf(s1, c, (gc + 1 <= grow) ? 0.f : -1.0e6f) - m_new;
+              x2 = fmaf(s2, c, (gc + 2 <= grow) ? 0.f : -1.0e6f) - m_new;
+              x3 = fmaf(s3, c, (gc + 3 <= grow) ? 0.f : -1.0e6f) - m_new;
+            } else {
+              x0 = fmaf(s0, c, -m_new);
+              x1 = fmaf(s1, c, -m_new);
+              x2 = fmaf(s2, c, -m_new);
+              x3 = fmaf(s3, c, -m_new);
+            }
+            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
+            lsum += (p0 + p1) + (p2 + p3);
+            if constexpr (FULL) {
+              int q0, q1, q2, q3;
+              if constexpr (PRNE) {
+                q0 = min(__float2int_rn(p0 * 127.f), 127);
+                q1 = min(__float2int_rn(p1 * 127.f), 127);
+                q2 = min(__float2int_rn(p2 * 127.f), 127);
+                q3 = min(__float2int_rn(p3 * 127.f), 127);
+              } else {
+                const __half2 k127 = __float2half2_rn(127.f), khalf = __float2half2_rn(0.5f);
+                const __half2 h01 = __hadd2(__hmul2(__floats2half2_rn(p0, p1), k127), khalf);
+                const __half2 h23 = __hadd2(__hmul2(__floats2half2_rn(p2, p3), k127), khalf);
+                q0 = __half2int_rz(__low2half(h01));
+                q1 = __half2int_rz(__high2half(h01));
+                q2 = __half2int_rz(__low2half(h23));
+                q3 = __half2int_rz(__high2half(h23));
+              }
+              pk[i] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
+                      ((uint32_t)(q3 & 0xff) << 24);
+            } else {
+              const __half2 h01 = __floats2half2_rn(p0, p1);
+              const __half2 h23 = __floats2half2_rn(p2, p3);
+              pk[2 * i] = *reinterpret_cast<const uint32_t*>(&h01);
+              pk[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+            }
+          }
+          if constexpr (FULL) {
+            // 32 int8 = two 16-byte chunks of this row
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const uint32_t off = swz_off<G>(row, cc * 2 + h);
+              *reinterpret_cast<uint4*>(sP_gen + off) = make_uint4(pk[4 * h], pk[4 * h + 1], pk[4 * h + 2], pk[4 * h + 3]);
+            }
+            if (dbg_here && p.dbg_p) {
+              uint32_t* dp = reinterpret_cast<uint32_t*>(reinterpret_cast<int8_t*>(p.dbg_p) + row * G + cc * 32);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) dp[i] = pk[i];
+            }
+          } else {
+            // 32 fp16 = four 16-byte chunks; columns [64*blk, 64*blk+64) live in block blk of 128 rows x 128 B
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              const int col = cc * 32 + h * 8;
+              const uint32_t off = (col >> 6) * (kBM * 128) + swz_off<128>(row, (col & 63) >> 3);
+              *reinterpret_cast<uint4*>(sP_gen + off) = make_uint4(pk[4 * h], pk[4 * h + 1], pk[4 * h + 2], pk[4 * h + 3]);
+            }
+            if (dbg_here && p.dbg_p) {
+              uint32_t* dp = reinterpret_cast<uint32_t*>(reinterpret_cast<__half*>(p.dbg_p) + row * G + cc * 32);
+#pragma unroll
+              for (int i = 0; i < 16; ++i) dp[i] = pk[i];
+            }
+          }
+        }
+        // P visible to the tensor core's shared-memory reads; S fully read
+        fence_proxy_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR(B_PFULL));
+        l_i = l_i * alpha + lsum;
+        m_i = m_new;
+
+        // ---- correction: acc = acc*alpha + O_j * s_v/127
+        ok = mbar_wait(BAR(B_OFULL), step_it & 1, abort_flag, p.status, code_hi | W_O_FULL);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t r[32];
+          tmem_ld32(tO + lane_sel + cc * 32, r);
+          tmem_ld_wait(r);
+          if constexpr (FULL) {
+            const float4* v4 = reinterpret_cast<const float4*>(vsd_s + cc * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 vv = v4[i];
+              acc[cc * 32 + 4 * i + 0] = fmaf(__int2float_rn((int)r[4 * i + 0]), vv.x, acc[cc * 32 + 4 * i + 0] * alpha);
+              acc[cc * 32 + 4 * i + 1] = fmaf(__int2float_rn((int)r[4 * i + 1]), vv.y, acc[cc * 32 + 4 * i + 1] * alpha);
+              acc[cc * 32 + 4 * i + 2] = fmaf(__int2float_rn((int)r[4 * i + 2]), vv.z, acc[cc * 32 + 4 * i + 2] * alpha);
+              acc[cc * 32 + 4 * i + 3] = fmaf(__int2float_rn((int)r[4 * i + 3]), vv.w, acc[cc * 32 + 4 * i + 3] * alpha);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              acc[cc * 32 + i] = fmaf(acc[cc * 32 + i], alpha, __uint_as_float(r[i]));
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR(B_OEMPTY));
+      }
+      if (!ok) break;
+
+      // ---- epilogue
+      if (p.state_out) {
+        p.st_m[rowg] = m_i;
+        p.st_l[rowg] = l_i;
+        float4* a4 = reinterpret_cast<float4*>(p.st_acc + rowg * D);
+#pragma unroll
+        for (int i = 0; i < D / 4; ++i) a4[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+      }
+      if (p.write_o) {
+        __half* orow = p.o + (long long)t.b * p.o_sb + (long long)t.h * p.o_sh + (long long)(t.mb * kBM + row) * p.o_sn;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const __half2 h = __floats2half2_rn(acc[8 * i + 2 * e] / l_i, acc[8 * i + 2 * e + 1] / l_i);
+            w[e] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+          *reinterpret_cast<uint4*>(orow + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        if (p.lse) p.lse[rowg] = m_i + log2f(l_i);
+      }
+    }
+  }
+
+  // -------------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ============================================================================
+// host side
+// ============================================================================
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// [B,H,N,D] tensor, element strides for (B,H,N); box = (box_d, box_rows, 1, 1)
+static int make_tmap(CUtensorMap* tm, const void* base, int esize, const int64_t* stride, int B, int H, int N, int D,
+                     int box_d, int box_rows, CUtensorMapSwizzle swz) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return set_error(INTFA_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)(stride[2] * esize), (cuuint64_t)(stride[1] * esize),
+                           (cuuint64_t)(stride[0] * esize)};
+  cuuint32_t box[4] = {(cuuint32_t)box_d, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(tm, esize == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(INTFA_ERR_CUDA, "cuTensorMapEncodeTiled failed (CUresult %d)", (int)r);
+  return INTFA_OK;
+}
+
+template <int D, int G, bool FULL, bool PRNE>
+static int launch(const IntfaFwdParams* a, const KParams& kp, cudaStream_t stream) {
+  using C = Cfg<D, G, FULL>;
+  CUtensorMap tmQ, tmK, tmV;
+  const CUtensorMapSwizzle swzD = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  int rc;
+  if ((rc = make_tmap(&tmQ, a->q, 1, a->q_stride, a->B, a->H, a->Nq, D, D, kBM, swzD))) return rc;
+  if ((rc = make_tmap(&tmK, a->k, 1, a->k_stride, a->B, a->H, a->Nk, D, D, G, swzD))) return rc;
+  if constexpr (FULL) {
+    if ((rc = make_tmap(&tmV, a->v, 1, a->v_stride, a->B, a->H, a->Nk, D, D, G, swzD))) return rc;
+  } else {
+    if ((rc = make_tmap(&tmV, a->v, 2, a->v_stride, a->B, a->H, a->Nk, D, 64, G, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  }
+  auto kern = intfa_fwd_kernel<D, G, FULL, PRNE>;
+  static bool attr_done = false;     // per instantiation; the attribute is per device, so set it every time a device changes
+  static int attr_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_done || attr_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return set_error(INTFA_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    attr_done = true;
+    attr_dev = dev;
+  }
+  const int sms = sm_count_cached();
+  if (sms <= 0) return set_error(INTFA_ERR_CUDA, "cannot query SM count");
+  const int ctas_per_sm = (C::SMEM_BYTES + 1024) * 2 <= 227 * 1024 ? 2 : 1;
+  int grid = sms * ctas_per_sm;
+  if (grid > kp.num_tiles) grid = kp.num_tiles;
+  kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, kp);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(INTFA_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(e));
+  return INTFA_OK;
+}
+
+int fwd_dispatch(const IntfaFwdParams* a, cudaStream_t stream) {
+  KParams kp;
+  kp.qs = a->q_scale; kp.ks = a->k_scale; kp.vs = a->v_scale;
+  kp.o = reinterpret_cast<__half*>(a->o);
+  kp.o_sb = a->o_stride[0]; kp.o_sh = a->o_stride[1]; kp.o_sn = a->o_stride[2];
+  kp.qs_sb = a->qs_stride[0]; kp.qs_sh = a->qs_stride[1];
+  kp.ks_sb = a->ks_stride[0]; kp.ks_sh = a->ks_stride[1];
+  kp.vs_sb = a->vs_stride[0]; kp.vs_sh = a->vs_stride[1]; kp.vs_sd = a->vs_stride[2];
+  kp.B = a->B; kp.H = a->H; kp.Nq = a->Nq; kp.Nk = a->Nk;
+  kp.causal = a->causal ? 1 : 0;
+  kp.c = a->sm_scale * 1.44269504f;          // fp32 product, flash_atten_full_int8.py:156-157
+  kp.q_off = a->q_offset; kp.kv_off = a->kv_offset;
+  kp.lse = a->lse_out; kp.st_m = a->state_m; kp.st_l = a->state_l; kp.st_acc = a->state_acc;
+  kp.state_in = a->state_in; kp.state_out = a->state_out; kp.write_o = a->write_o;
+  kp.dbg_s = a->dbg_s; kp.dbg_p = a->dbg_p; kp.dbg_tile = a->dbg_tile; kp.dbg_step = a->dbg_step;
+  kp.status = a->status;
+  kp.MB = a->Nq / kBM;
+  kp.num_tiles = a->B * a->H * kp.MB;
+  const bool full = a->variant == INTFA_VARIANT_FULL;
+  const bool rne = full && a->p_round == 1;
+  const int D = a->D, G = a->G;
+#define INTFA_CASE(DD, GG)                                                       \
+  if (D == DD && G == GG) {                                                      \
+    if (full) return rne ? launch<DD, GG, true, true>(a, kp, stream)             \
+                         : launch<DD, GG, true, false>(a, kp, stream);           \
+    return launch<DD, GG, false, false>(a, kp, stream);                          \
+  }
+  INTFA_CASE(128, 128)
+  INTFA_CASE(128, 64)
+  INTFA_CASE(64, 64)
+#undef INTFA_CASE
+  return set_error(INTFA_ERR_UNSUPPORTED, "unsupported (D=%d, G=%d): supported are (128,128), (128,64), (64,64)", D, G);
+}
+
+}  // namespace intfa

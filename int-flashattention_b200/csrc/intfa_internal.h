@@ -1,0 +1,43 @@
+// Internal declarations shared by the translation units of libintfa.so.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/intfa.h"
+
+namespace intfa {
+
+// Arguments of the attention kernel (plain data, passed by value).
+struct KParams {
+  const float* qs; const float* ks; const float* vs;
+  __half* o;
+  long long o_sb, o_sh, o_sn;
+  long long qs_sb, qs_sh, ks_sb, ks_sh, vs_sb, vs_sh, vs_sd;
+  int B, H, Nq, Nk;
+  int causal;
+  float c;                       // sm_scale * 1.44269504 (fp32)
+  long long q_off, kv_off;
+  float* lse; float* st_m; float* st_l; float* st_acc;
+  int state_in, state_out, write_o;
+  int* dbg_s; void* dbg_p; int dbg_tile, dbg_step;
+  int* status;
+  int MB, num_tiles;
+};
+
+// Records the calling thread's last error (printf-style) and returns `code`.
+int set_error(int code, const char* fmt, ...);
+// SM count of the current device, cached per device; <=0 on failure.
+int sm_count_cached();
+
+int fwd_dispatch(const IntfaFwdParams* a, cudaStream_t stream);
+int quant_pertoken(const void* x, const int64_t* st, void* x8, float* scale, int B, int H, int N, int D,
+                   cudaStream_t stream);
+int quant_v(const void* v, const int64_t* st, void* v8, float* scale, int mode, int B, int H, int N, int D,
+            void* workspace, cudaStream_t stream);
+int v_colmax(const void* v, const int64_t* st, void* colmax, int B, int H, int N, int D, cudaStream_t stream);
+int v_quant_from_colmax(const void* v, const int64_t* st, const void* colmax, void* v8, float* scale, int mode, int B,
+                        int H, int N, int D, cudaStream_t stream);
+int scales_f16_to_f32(const void* src, float* dst, long long n, cudaStream_t stream);
+
+}  // namespace intfa

@@ -1,0 +1,251 @@
+// Fused quantisation prologue (HBM-bound): fp16 -> int8 with absmax scales.
+//
+// Bit-exact restatement of the reference quantisers, whose arithmetic follows the fp16
+// input dtype (benchmark.py:96-107):
+//   amax  = max |x|                       (exact in fp16)
+//   scale = fp16( fp32(amax) / 127 )      (IEEE fp32 division, then round-to-nearest fp16)
+//   q     = int8( rint( fp16( fp32(x) / fp32(scale) ) ) )   (rint = half-to-even, as torch.round)
+// Scales are written as fp32 holding the fp16-representable value.  amax == 0 gives
+// scale 0 and q 0 (the reference computes 0/0 there).
+//
+// Each row of D fp16 is read by D/8 lanes with one 128-bit load per lane; the row/column
+// maxima are reduced with warp shuffles.  Per-token: one pass.  V (per-channel or
+// per-(batch,head)): a column-absmax pass into a small scratch array (atomicMax on the
+// bit pattern of non-negative floats), then the quantising pass.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "intfa_internal.h"
+
+namespace intfa {
+
+__device__ __forceinline__ float scale_from_amax(float amax) {
+  return __half2float(__float2half_rn(__fdiv_rn(amax, 127.0f)));
+}
+__device__ __forceinline__ int quant_one(float x, float s) {
+  if (s == 0.f) return 0;
+  const float t = __half2float(__float2half_rn(__fdiv_rn(x, s)));
+  return (int)rintf(t);
+}
+__device__ __forceinline__ float amax8(const uint4& v) {
+  const __half2* h = reinterpret_cast<const __half2*>(&v);
+  __half2 m = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+  return fmaxf(__low2float(m), __high2float(m));
+}
+__device__ __forceinline__ uint2 quant8(const uint4& v, const float* s) {
+  const __half* h = reinterpret_cast<const __half*>(&v);
+  uint32_t w[2] = {0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int q = quant_one(__half2float(h[i]), s[i]);
+    w[i >> 2] |= (uint32_t)(q & 0xff) << (8 * (i & 3));
+  }
+  return make_uint2(w[0], w[1]);
+}
+
+template <int D>
+__global__ void __launch_bounds__(256) quant_pertoken_kernel(const __half* __restrict__ x, long long sB, long long sH,
+                                                             long long sN, int8_t* __restrict__ x8,
+                                                             float* __restrict__ scale, int H, int N,
+                                                             long long total_rows) {
+  constexpr int LPR = D / 8;         // lanes per row
+  constexpr int RPW = 32 / LPR;      // rows per warp
+  const int lane = threadIdx.x & 31;
+  const int sub = lane % LPR;
+  const long long warp_g = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long row0 = warp_g * RPW; row0 < total_rows; row0 += nwarps * RPW) {
+    const long long row = row0 + lane / LPR;
+    const bool live = row < total_rows;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (live) {
+      const long long bh = row / N;
+      const int n = (int)(row - bh * N);
+      const int b = (int)(bh / H), h = (int)(bh - (long long)b * H);
+      v = *reinterpret_cast<const uint4*>(x + b * sB + h * sH + n * sN + sub * 8);
+    }
+    float a = amax8(v);
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    const float s = scale_from_amax(a);
+    if (live) {
+      const float sv[8] = {s, s, s, s, s, s, s, s};
+      *reinterpret_cast<uint2*>(x8 + row * D + sub * 8) = quant8(v, sv);
+      if (sub == 0) scale[row] = s;
+    }
+  }
+}
+
+// column absmax of one (batch, head) slab chunk -> atomicMax into colmax[bh*D + ch]
+template <int D>
+__global__ void __launch_bounds__(256) v_colmax_kernel(const __half* __restrict__ x, long long sB, long long sH,
+                                                       long long sN, unsigned int* __restrict__ colmax, int H, int N,
+                                                       int rows_per_cta) {
+  constexpr int LPR = D / 8;
+  constexpr int RPW = 32 / LPR;
+  __shared__ float red[8][D];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int sub = lane % LPR;
+  const int bh = blockIdx.y;
+  const int b = bh / H, h = bh - b * H;
+  const __half* base = x + b * sB + h * sH + sub * 8;
+  const int r_begin = blockIdx.x * rows_per_cta;
+  const int r_end = min(N, r_begin + rows_per_cta);
+  __half2 m[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) m[i] = __float2half2_rn(0.f);
+  for (int r = r_begin + warp * RPW + lane / LPR; r < r_end; r += nw * RPW) {
+    const uint4 v = *reinterpret_cast<const uint4*>(base + r * sN);
+    const __half2* hv = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) m[i] = __hmax2(m[i], __habs2(hv[i]));
+  }
+  float f[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __low2float(m[i]);
+    f[2 * i + 1] = __high2float(m[i]);
+  }
+#pragma unroll
+  for (int o = LPR; o < 32; o <<= 1)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = fmaxf(f[i], __shfl_xor_sync(0xffffffffu, f[i], o));
+  if (lane < LPR)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[warp][sub * 8 + i] = f[i];
+  __syncthreads();
+  for (int ch = threadIdx.x; ch < D; ch += blockDim.x) {
+    float a = 0.f;
+    for (int w = 0; w < nw; ++w) a = fmaxf(a, red[w][ch]);
+    atomicMax(colmax + (long long)bh * D + ch, __float_as_uint(a));
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(256) v_quant_kernel(const __half* __restrict__ x, long long sB, long long sH,
+                                                      long long sN, const unsigned int* __restrict__ colmax,
+                                                      int8_t* __restrict__ x8, float* __restrict__ scale,
+                                                      int per_channel, int H, int N, int rows_per_cta) {
+  constexpr int LPR = D / 8;
+  constexpr int RPW = 32 / LPR;
+  __shared__ float s_scale[D];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int sub = lane % LPR;
+  const int bh = blockIdx.y;
+  const int b = bh / H, h = bh - b * H;
+  if (threadIdx.x < 32) {
+    // every channel's absmax; for the per-(batch,head) mode reduce them to one
+    float a[D / 32];
+    float all = 0.f;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) {
+      a[i] = __uint_as_float(colmax[(long long)bh * D + lane + 32 * i]);
+      all = fmaxf(all, a[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) all = fmaxf(all, __shfl_xor_sync(0xffffffffu, all, o));
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) s_scale[lane + 32 * i] = scale_from_amax(per_channel ? a[i] : all);
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    if (per_channel) {
+      for (int ch = threadIdx.x; ch < D; ch += blockDim.x) scale[(long long)bh * D + ch] = s_scale[ch];
+    } else if (threadIdx.x == 0) {
+      scale[bh] = s_scale[0];
+    }
+  }
+  float sv[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) sv[i] = s_scale[sub * 8 + i];
+  const __half* base = x + b * sB + h * sH + sub * 8;
+  int8_t* obase = x8 + (long long)bh * N * D + sub * 8;
+  const int r_begin = blockIdx.x * rows_per_cta;
+  const int r_end = min(N, r_begin + rows_per_cta);
+  for (int r = r_begin + warp * RPW + lane / LPR; r < r_end; r += nw * RPW) {
+    const uint4 v = *reinterpret_cast<const uint4*>(base + r * sN);
+    *reinterpret_cast<uint2*>(obase + (long long)r * D) = quant8(v, sv);
+  }
+}
+
+__global__ void scales_f16_to_f32_kernel(const __half* __restrict__ src, float* __restrict__ dst, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    dst[i] = __half2float(src[i]);
+}
+
+static int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(INTFA_ERR_CUDA, "%s launch: %s", what, cudaGetErrorString(e));
+  return INTFA_OK;
+}
+
+int quant_pertoken(const void* x, const int64_t* st, void* x8, float* scale, int B, int H, int N, int D,
+                   cudaStream_t stream) {
+  const long long rows = (long long)B * H * N;
+  const int sms = sm_count_cached();
+  if (sms <= 0) return set_error(INTFA_ERR_CUDA, "cannot query SM count");
+  const int rpw = 32 / (D / 8);
+  long long want = (rows + 8LL * rpw - 1) / (8LL * rpw);          // CTAs of 8 warps, one row group each
+  const int grid = (int)(want < (long long)sms * 8 ? (want < 1 ? 1 : want) : (long long)sms * 8);
+  if (D == 128)
+    quant_pertoken_kernel<128><<<grid, 256, 0, stream>>>((const __half*)x, st[0], st[1], st[2], (int8_t*)x8, scale, H, N, rows);
+  else
+    quant_pertoken_kernel<64><<<grid, 256, 0, stream>>>((const __half*)x, st[0], st[1], st[2], (int8_t*)x8, scale, H, N, rows);
+  return check_launch("quant_pertoken");
+}
+
+static int v_grid(int BH, int N, int sms, int* rows_per_cta) {
+  // chunks per (batch, head): enough CTAs to fill the machine a few times over, at least 256 rows each
+  int chunks = (sms * 8 + BH - 1) / BH;
+  const int max_chunks = (N + 255) / 256;
+  if (chunks > max_chunks) chunks = max_chunks;
+  if (chunks < 1) chunks = 1;
+  *rows_per_cta = (N + chunks - 1) / chunks;
+  return chunks;
+}
+
+int v_colmax(const void* v, const int64_t* st, void* colmax, int B, int H, int N, int D, cudaStream_t stream) {
+  const int sms = sm_count_cached();
+  if (sms <= 0) return set_error(INTFA_ERR_CUDA, "cannot query SM count");
+  int rows_per_cta;
+  dim3 grid(v_grid(B * H, N, sms, &rows_per_cta), B * H);
+  if (D == 128)
+    v_colmax_kernel<128><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (unsigned int*)colmax, H, N, rows_per_cta);
+  else
+    v_colmax_kernel<64><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (unsigned int*)colmax, H, N, rows_per_cta);
+  return check_launch("v_colmax");
+}
+
+int v_quant_from_colmax(const void* v, const int64_t* st, const void* colmax, void* v8, float* scale, int mode, int B,
+                        int H, int N, int D, cudaStream_t stream) {
+  const int sms = sm_count_cached();
+  if (sms <= 0) return set_error(INTFA_ERR_CUDA, "cannot query SM count");
+  int rows_per_cta;
+  dim3 grid(v_grid(B * H, N, sms, &rows_per_cta), B * H);
+  const int pc = mode == INTFA_VSCALE_PER_CHANNEL;
+  if (D == 128)
+    v_quant_kernel<128><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (const unsigned int*)colmax, (int8_t*)v8, scale, pc, H, N, rows_per_cta);
+  else
+    v_quant_kernel<64><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (const unsigned int*)colmax, (int8_t*)v8, scale, pc, H, N, rows_per_cta);
+  return check_launch("v_quant");
+}
+
+int quant_v(const void* v, const int64_t* st, void* v8, float* scale, int mode, int B, int H, int N, int D,
+            void* workspace, cudaStream_t stream) {
+  cudaError_t e = cudaMemsetAsync(workspace, 0, (size_t)B * H * D * sizeof(unsigned int), stream);
+  if (e != cudaSuccess) return set_error(INTFA_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+  int rc = v_colmax(v, st, workspace, B, H, N, D, stream);
+  if (rc) return rc;
+  return v_quant_from_colmax(v, st, workspace, v8, scale, mode, B, H, N, D, stream);
+}
+
+int scales_f16_to_f32(const void* src, float* dst, long long n, cudaStream_t stream) {
+  if (n <= 0) return INTFA_OK;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 4096) blocks = 4096;
+  scales_f16_to_f32_kernel<<<(int)blocks, 256, 0, stream>>>((const __half*)src, dst, n);
+  return check_launch("scales_f16_to_f32");
+}
+
+}  // namespace intfa
