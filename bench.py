@@ -1,0 +1,329 @@
+#!/usr/bin/env python
+"""Benchmark of the INT8 FlashAttention forward hot path.
+
+One "step" = one pass of the hot path over one batch of synthetic input: the fused quantisation
+prologue (fp16 Q/K/V -> int8 + scales) followed by the attention forward, on the workload the
+headline metric is quoted on (full-int8, batch 4, heads 32, seq 8192, head_dim 128, non-causal,
+sm_scale 1/sqrt(128), Q/K/V fp16 ~ N(0,1) from a seed).  With --gpus N (launched under
+torch.distributed.run) every rank processes its own batch of that size -- (batch, head) pairs are
+independent, so there is no data-path collective -- and the reported value is the work of all
+ranks over the slowest rank's time (weak scaling).
+
+Prints ONE JSON line.  `--impl reference` times the reference's CPU math (the oracle port) on a
+bounded sample of the same workload on the host cores instead.
+"""
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (variant, B, H, N, D, causal, std, outlier)
+    "c2_full_b4_h32_n8192_d128": ("full", 4, 32, 8192, 128, False, 1.0, False),
+    "c3_half_b8_h32_n4096_d128_causal": ("half", 8, 32, 4096, 128, True, 1.0, True),
+    "c4shard_full_b8_h64_n4096_d128": ("full", 8, 64, 4096, 128, False, 1.0, False),
+    "c1_full_b1_h4_n512_d64": ("full", 1, 4, 512, 64, False, 1.0, False),
+    # small cases of the same kernels for profiler captures (a few hundred MB on the device)
+    "prof_full_b2_h16_n4096_d128": ("full", 2, 16, 4096, 128, False, 1.0, False),
+    "prof_half_b2_h16_n4096_d128_causal": ("half", 2, 16, 4096, 128, True, 1.0, True),
+}
+DEFAULT_WORKLOAD = "c2_full_b4_h32_n8192_d128"
+METRIC = "INT8 attn fwd effective TOPS (4*B*H*N^2*d / t, halved for causal), prologue included"
+
+
+def attn_ops(B, H, N, D, causal):
+    ops = 4.0 * B * H * N * N * D
+    return ops / 2 if causal else ops
+
+
+def prologue_bytes(B, H, N, D, full):
+    """Algorithmic bytes of the quantisation prologue: every input read once, every output written once."""
+    E = B * H * N * D
+    if full:
+        return 3 * E * 2 + 3 * E + (2 * B * H * N + B * H * D) * 4
+    return 2 * E * 2 + 2 * E + 2 * B * H * N * 4
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return json.load(open(p)), "measured"
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs (read-only queries)."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            c = [x.strip() for x in r.split(",")]
+            if len(c) < 7:
+                continue
+            try:
+                sm.append(float(c[0]))
+                mx.append(float(c[1]))
+                power.append(float(c[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, c[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def synth(B, H, N, D, std, outlier, seed, device):
+    g = torch.Generator(device=device).manual_seed(seed)
+    q, k, v = (std * torch.randn(B, H, N, D, device=device, generator=g, dtype=torch.float32) for _ in range(3))
+    if outlier:
+        ch = int(torch.randint(0, D, (1,), device=device, generator=g))
+        q[..., ch] *= 20
+        k[..., ch] *= 20
+    return q.half(), k.half(), v.half()
+
+
+def cpu_reference_leg(workload, budget_s=20.0, max_heads=8):
+    """The reference's PyTorch/Triton math restated for CPU (oracle port), timed on whole (batch, head)
+    slices of the workload with all host threads; the bounded sample is scaled to the metric's unit."""
+    from oracle import intfa_oracle as O
+    variant, B, H, N, D, causal, std, outlier = WORKLOADS[workload]
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    sm = D ** -0.5
+    q, k, v = synth(1, 1, N, D, std, outlier, 4242, "cpu")
+    heads, t_total = 0, 0.0
+    while heads < max_heads and (heads == 0 or t_total < budget_s):
+        t0 = time.perf_counter()
+        q8, qs = O.quant_pertoken(q)
+        k8, ks = O.quant_pertoken(k)
+        if variant == "full":
+            v8, vs = O.quant_perchannel(v)
+            O.attention_full_int8(q8, k8, v8, qs, ks, vs, causal, sm, G=128 if D >= 128 else 64)
+        else:
+            O.attention_int8(q8, k8, v, qs, ks, causal, sm, G=128 if D >= 128 else 64)
+        t_total += time.perf_counter() - t0
+        heads += 1
+    tops = attn_ops(1, 1, N, D, causal) * heads / t_total / 1e12
+    return {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port",
+            "sample": "%d of %d (batch,head) slices of %s, %.1f s of CPU work, prologue included"
+                      % (heads, B * H, workload, t_total),
+            "ms_per_slice": 1e3 * t_total / heads}
+
+
+def run_reference_arm(args, rank, world):
+    if rank != 0:
+        return
+    base = cpu_reference_leg(args.workload, budget_s=8.0, max_heads=4)      # warm-up of the host path
+    t0 = time.perf_counter()
+    vals = [cpu_reference_leg(args.workload, budget_s=4.0, max_heads=2) for _ in range(max(1, min(args.steps, 5)))]
+    dt = time.perf_counter() - t0
+    value = statistics.mean(v["value"] for v in vals)
+    variant, B, H, N, D, causal, std, outlier = WORKLOADS[args.workload]
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": args.gpus,
+            "steps": len(vals), "warmup": 1, "ms_per_step": 1e3 * dt / len(vals), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "s8", "data": "synthetic",
+            "config": {"workload": args.workload, "variant": variant, "B": B, "H": H, "N": N, "D": D, "causal": causal,
+                       "note": "each step = bounded sample of whole (batch,head) slices on host cores"},
+            "cpu_baseline": {"value": value, "unit": "TOPS", "cores": base["cores"], "kind": "port",
+                             "sample": vals[0]["sample"]},
+            "e2e": {"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch.distributed as dist
+    pkg = importlib.import_module("int-flashattention_b200")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    variant, B, H, N, D, causal, std, outlier = WORKLOADS[args.workload]
+    full = variant == "full"
+    sm_scale = D ** -0.5
+    q, k, v = synth(B, H, N, D, std, outlier, 1000 + rank, dev)
+
+    def step():
+        return pkg.int_flash_attention(q, k, v, causal, sm_scale, variant=variant)
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+        torch.cuda.synchronize(dev)
+
+    for _ in range(args.warmup):
+        o = step()
+    pkg.check_status(dev)
+
+    # ---- device-timed region: K steps, plus per-step events around the attention launch alone
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    a1 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    barrier()
+    ev0.record()
+    for i in range(args.steps):
+        q8, qs = pkg.quant_pertoken(q)
+        k8, ks = pkg.quant_pertoken(k)
+        if full:
+            v8, vs = pkg.quant_perchannel(v)
+            a0[i].record()
+            o = pkg.attention_full_int8(q8, k8, v8, qs, ks, vs, causal, sm_scale)
+        else:
+            a0[i].record()
+            o = pkg.attention_int8(q8, k8, v, qs, ks, causal, sm_scale)
+        a1[i].record()
+    ev1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = ev0.elapsed_time(ev1)
+    attn_ms = statistics.mean(x.elapsed_time(y) for x, y in zip(a0, a1))
+    pkg.check_status(dev)
+    t = torch.tensor([ms_total, attn_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, attn_ms = float(t[0]), float(t[1])
+    ms_per_step = ms_total / args.steps
+    ops_step = attn_ops(B, H, N, D, causal)
+    value = ops_step * world / (ms_per_step * 1e-3) / 1e12
+    launches_per_step = 5 if full else 3            # 2x per-token quant (+ V colmax + V quant) + attention
+
+    # ---- end-to-end through the public API with HOST buffers (pinned): H2D of q,k,v and D2H of o every step
+    e2e = None
+    if not args.no_e2e:
+        hq, hk, hv = (x.cpu().pin_memory() for x in (q, k, v))
+        ho = torch.empty((B, H, N, D), dtype=torch.float16).pin_memory()
+        dq, dk, dv = (torch.empty_like(x) for x in (q, k, v))
+
+        def e2e_step():
+            dq.copy_(hq, non_blocking=True)
+            dk.copy_(hk, non_blocking=True)
+            dv.copy_(hv, non_blocking=True)
+            out = pkg.int_flash_attention(dq, dk, dv, causal, sm_scale, variant=variant)
+            ho.copy_(out, non_blocking=True)
+
+        n_e2e = max(3, min(args.steps, 10))
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        barrier()
+        te = torch.tensor([e0.elapsed_time(e1) / n_e2e], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e = {"value": ops_step * world / (float(te[0]) * 1e-3) / 1e12, "unit": "TOPS",
+               "ms_per_step": float(te[0]), "steps": n_e2e,
+               "h2d_bytes_per_step": 3 * q.numel() * 2, "d2h_bytes_per_step": ho.numel() * 2}
+        del hq, hk, hv, ho, dq, dk, dv
+
+    if rank == 0:
+        peaks, src = measured_peaks()
+        peak_int8 = 2.0 * peaks["bf16_tflops_sustained"]
+        achieved = ops_step / (attn_ms * 1e-3) / 1e12
+        prof = {}
+        pj = os.path.join(ROOT, "profiles", "roofline_inputs.json")
+        if os.path.exists(pj):
+            prof = json.load(open(pj)).get(args.workload, {})
+        roofline = {"bound": "tensor", "kernel": "intfa_fwd_kernel", "achieved": achieved, "peak": peak_int8,
+                    "unit": "TFLOP/s", "frac": achieved / peak_int8,
+                    "traffic": prof.get("attn_dram_bytes_per_launch"),
+                    "peak_source": "2 x MEASURED_PEAKS.bf16_tflops_sustained (%s; int8 dense rate = 2x bf16)" % src,
+                    "kernel_ms": attn_ms,
+                    "prologue": {"bound": "hbm", "ms": ms_per_step - attn_ms,
+                                 "achieved": prologue_bytes(B, H, N, D, full) / ((ms_per_step - attn_ms) * 1e-3) / 1e9,
+                                 "peak": peaks["hbm_gbs"], "unit": "GB/s"}}
+        roofline["prologue"]["frac"] = roofline["prologue"]["achieved"] / peaks["hbm_gbs"]
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            cpu = cpu_reference_leg(args.workload)
+        line = {"metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "s8", "data": "synthetic",
+                "config": {"workload": args.workload, "variant": variant, "B_per_gpu": B, "H": H, "N": N, "D": D,
+                           "causal": causal, "sm_scale": sm_scale, "quantised_in_step": True,
+                           "l2": "inputs exceed L2 (%.0f MiB of fp16 Q/K/V per step)" % (3 * q.numel() * 2 / 2 ** 20),
+                           "sharding": "batch x heads, no collective"},
+                "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
+                "roofline": roofline, "cpu_baseline": cpu,
+                "pct_of_nominal_int8_peak": 100.0 * achieved / 4500.0}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -85,12 +85,12 @@ def _scales_f32(s):
 def _fwd(variant, q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, *, G=None, p_round="triton",
          state=None, q_offset=0, kv_offset=0, return_state=False, return_lse=False, write_o=True,
          debug_tap=None):
-    lib = _lib.load()
-    _need_cuda(q, k, v, q_scale, k_scale, v_scale)
     # shape constraints, as flash_atten_full_int8.py:189-193
     HEAD_DIM_Q, HEAD_DIM_K, HEAD_DIM_V = q.shape[-1], k.shape[-1], v.shape[-1]
     assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V
     assert HEAD_DIM_K in {16, 32, 64, 128, 256}
+    _need_cuda(q, k, v, q_scale, k_scale, v_scale)
+    lib = _lib.load()
     full = variant == "full"
     if q.dtype != torch.int8 or k.dtype != torch.int8:
         raise TypeError("q and k must be int8")

@@ -1,0 +1,321 @@
+"""GPU parity: every call goes through libintfa.so's C ABI (via the ctypes operator layer) and is
+compared with the CPU oracle on the same seeded inputs, and with the reference's own outputs
+stored under tests/golden/.
+
+Tolerances.  Integer/byte results (quantised tensors, scales, the int32 QK^T tile) are bit-exact.
+The fp16 output is held to the bar stated for this path: max-abs <= 1e-2 and mean-relative
+(mean|d| / mean|ref|) <= 1e-3 against the reference's int8 output on the same inputs; where the
+running-max granularity G is pinned to the oracle's the observed differences are far smaller
+(ex2.approx vs exp2, fma contraction, reduction order), so tighter bounds are asserted too.
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden_names, load_golden, make_qkv
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS, MEAN_REL = 1e-2, 1e-3          # the stated bar
+TIGHT_MAX_ABS, TIGHT_MEAN_REL = 4e-3, 3e-4
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    return torch.device("cuda:0")
+
+
+def _close(oracle, out, ref, tight=True):
+    e = oracle.err_metrics(out.cpu(), ref.cpu())
+    assert e["max_abs"] <= (TIGHT_MAX_ABS if tight else MAX_ABS), e
+    assert e["mean_rel"] <= (TIGHT_MEAN_REL if tight else MEAN_REL), e
+    return e
+
+
+# ------------------------------------------------------------------------------- quantisation
+@pytest.mark.parametrize("B,H,N,D", [(1, 4, 512, 64), (2, 3, 256, 128), (1, 1, 8, 128), (1, 2, 1000, 64)])
+def test_quant_pertoken_bit_exact(B, H, N, D, pkg, oracle, dev):
+    q, _, _ = make_qkv(21, B, H, N, D)
+    q[0, 0, 3] = 0                                   # an all-zero token
+    r8, rs = oracle.quant_pertoken(q)
+    r8, rs = oracle.zero_safe(r8, rs, q, -1)
+    g8, gs = pkg.quant_pertoken(q.to(dev))
+    assert gs.dtype == torch.float32
+    assert torch.equal(gs.cpu(), rs.float())
+    assert torch.equal(g8.cpu(), r8)
+
+
+def test_quant_pertoken_strided_input(pkg, oracle, dev):
+    x = make_qkv(22, 2, 256, 4, 128)[0]              # stored [B,N,H,D]
+    xt = x.permute(0, 2, 1, 3)                       # viewed  [B,H,N,D], non-contiguous
+    r8, rs = oracle.quant_pertoken(xt)
+    g8, gs = pkg.quant_pertoken(x.to(dev).permute(0, 2, 1, 3))
+    assert torch.equal(g8.cpu(), r8) and torch.equal(gs.cpu(), rs.float())
+
+
+@pytest.mark.parametrize("B,H,N,D", [(1, 4, 512, 64), (2, 3, 384, 128), (1, 1, 4096, 128)])
+def test_quant_v_bit_exact(B, H, N, D, pkg, oracle, dev):
+    _, _, v = make_qkv(23, B, H, N, D)
+    v[..., 5] = 0                                    # an all-zero channel
+    r8, rs = oracle.quant_perchannel(v)
+    r8, rs = oracle.zero_safe(r8, rs, v, -2)
+    g8, gs = pkg.quant_perchannel(v.to(dev))
+    assert torch.equal(gs.cpu(), rs.float()) and torch.equal(g8.cpu(), r8)
+    r8, rs = oracle.quant_pertensor(v)
+    g8, gs = pkg.quant_pertensor(v.to(dev))
+    assert torch.equal(gs.cpu(), rs.float()) and torch.equal(g8.cpu(), r8)
+
+
+# ------------------------------------------------------------------------------- integer tiles
+@pytest.mark.parametrize("D,G,variant", [(128, 128, "full"), (128, 64, "full"), (64, 64, "full"), (128, 128, "half"),
+                                         (128, 64, "half"), (64, 64, "half")])
+def test_qk_tile_and_p_tile(D, G, variant, pkg, oracle, dev):
+    """The int32 QK^T tile is bit-exact; the P tile of KV step 0 matches the restated rounding chain."""
+    B, H, N = 1, 2, 384
+    q, k, v = make_qkv(31, B, H, N, D)
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    v8, vs = oracle.quant_perchannel(v)
+    vv = v8 if variant == "full" else v
+    fn = pkg.attention_full_int8 if variant == "full" else pkg.attention_int8
+    for (h, mb, step) in [(0, 0, 0), (1, 2, 1), (1, 1, N // G - 1)]:
+        args = [q8.to(dev), k8.to(dev), vv.to(dev), qs.to(dev), ks.to(dev)] + ([vs.to(dev)] if variant == "full" else [])
+        _, (dbg_s, dbg_p) = fn(*args, False, D ** -0.5, G=G, debug_tap=(h * (N // 128) + mb, step))
+        pkg.check_status()
+        qt = q8[0, h, mb * 128:(mb + 1) * 128].float()
+        kt = k8[0, h, step * G:(step + 1) * G].float()
+        S = (qt @ kt.T).to(torch.int32)
+        assert torch.equal(dbg_s.cpu(), S)
+        if step == 0:
+            c = torch.tensor(oracle.qk_scale_f32(D ** -0.5))
+            s = S.float() * qs[0, h, mb * 128:(mb + 1) * 128, None].float()
+            s = s * ks[0, h, None, :G].float()
+            m = s.max(-1).values * c
+            p = torch.exp2(s * c - m[:, None])
+            if variant == "full":
+                want = oracle._p_to_int8(p, "triton")
+                diff = (dbg_p.cpu().int() - want.int()).abs()
+                assert diff.max() <= 1 and (diff != 0).float().mean() < 2e-3    # ex2.approx / fma ulps
+            else:
+                want = p.half()
+                assert (dbg_p.cpu().float() - want.float()).abs().max() <= 2e-3
+
+
+# ------------------------------------------------------------------------------- attention vs oracle
+CASES = [
+    # B, H, N, D, G, causal
+    (1, 4, 512, 64, 64, False),          # BASELINE config 0
+    (1, 2, 128, 128, 128, False),        # one tile
+    (2, 3, 384, 128, 128, False),
+    (1, 2, 512, 128, 64, False),
+    (1, 2, 512, 128, 128, True),
+    (1, 2, 512, 128, 64, True),
+    (2, 2, 384, 64, 64, True),
+    (1, 1, 2048, 128, 128, True),
+]
+
+
+@pytest.mark.parametrize("B,H,N,D,G,causal", CASES)
+def test_full_int8_matches_oracle(B, H, N, D, G, causal, pkg, oracle, dev):
+    q, k, v = make_qkv(41, B, H, N, D)
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    v8, vs = oracle.quant_perchannel(v)
+    sm = D ** -0.5
+    ref = oracle.attention_full_int8(q8, k8, v8, qs, ks, vs, causal, sm, G=G)
+    out = pkg.attention_full_int8(q8.to(dev), k8.to(dev), v8.to(dev), qs.to(dev), ks.to(dev), vs.to(dev), causal, sm, G=G)
+    pkg.check_status()
+    assert out.dtype == torch.float16 and out.shape == ref.shape
+    _close(oracle, out, ref)
+    # error against exact attention no worse than the oracle's own
+    ex = oracle.exact_attention(q, k, v, causal, sm)
+    e_out, e_ref = oracle.err_metrics(out.cpu(), ex), oracle.err_metrics(ref, ex)
+    assert e_out["mean_rel"] <= e_ref["mean_rel"] * 1.02 + 1e-6
+
+
+@pytest.mark.parametrize("B,H,N,D,G,causal", CASES)
+def test_half_int8_matches_oracle(B, H, N, D, G, causal, pkg, oracle, dev):
+    q, k, v = make_qkv(42, B, H, N, D, outlier=True)
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    sm = D ** -0.5
+    ref = oracle.attention_int8(q8, k8, v, qs, ks, causal, sm, G=G)
+    out = pkg.attention_int8(q8.to(dev), k8.to(dev), v.to(dev), qs.to(dev), ks.to(dev), causal, sm, G=G)
+    pkg.check_status()
+    _close(oracle, out, ref)
+
+
+@pytest.mark.parametrize("name", [n for n in golden_names() if "d32" not in n and "shipped" not in n])
+def test_against_reference_fixtures(name, pkg, oracle, dev):
+    """Outputs of the reference's own Triton kernels (interpreter run, BLOCK_N pinned) as the yardstick."""
+    g = load_golden(name)
+    G = g["block_n"]
+    t = lambda n: g[n].to(dev)
+    if g["variant"] == "full":
+        out = pkg.attention_full_int8(t("q8"), t("k8"), t("v8"), t("qs"), t("ks"), t("vs"), g["causal"], g["sm_scale"], G=G)
+    else:
+        out = pkg.attention_int8(t("q8"), t("k8"), t("v"), t("qs"), t("ks"), g["causal"], g["sm_scale"], G=G)
+    pkg.check_status()
+    _close(oracle, out, g["o"])
+    # and the prologue reproduces the reference's quantised tensors bit for bit
+    q8, qs = pkg.quant_pertoken(t("q"))
+    v8, vs = pkg.quant_pertensor(t("v"))
+    assert torch.equal(q8.cpu(), g["q8"]) and torch.equal(qs.cpu(), g["qs"].float())
+    assert torch.equal(v8.cpu(), g["v8"]) and torch.equal(vs.cpu(), g["vs"].float())
+
+
+def test_fp16_scales_and_per_tensor_v_scale(pkg, oracle, dev):
+    """Scales exactly as benchmark.py hands them over: fp16 [B,H,N] and fp16 [B,H]."""
+    q, k, v = make_qkv(43, 1, 2, 256, 128)
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    v8, vs = oracle.quant_pertensor(v)
+    assert qs.dtype == torch.float16 and vs.shape == (1, 2)
+    ref = oracle.attention_full_int8(q8, k8, v8, qs, ks, vs, False, 1.3, G=128)
+    a = pkg.attention_full_int8(q8.to(dev), k8.to(dev), v8.to(dev), qs.to(dev), ks.to(dev), vs.to(dev), False, 1.3)
+    b = pkg.attention_full_int8(q8.to(dev), k8.to(dev), v8.to(dev), qs.to(dev).float(), ks.to(dev).float(),
+                                vs.to(dev).float()[:, :, None].expand(1, 2, 128).contiguous(), False, 1.3)
+    pkg.check_status()
+    assert torch.equal(a, b)
+    _close(oracle, a, ref)
+
+
+def test_bench_style_inputs_run(pkg, oracle, dev):
+    """benchmark.py:56-63 feeds random int8 (incl. -128) and random, possibly negative, scales."""
+    g = torch.Generator().manual_seed(5)
+    B, H, N, D = 1, 2, 256, 64
+    q8, k8, v8 = (torch.randint(-128, 127, (B, H, N, D), dtype=torch.int8, generator=g) for _ in range(3))
+    qs, ks = (torch.randn(B, H, N, generator=g).half() * 0.01 for _ in range(2))
+    vs = torch.randn(B, H, generator=g).half()
+    ref = oracle.attention_full_int8(q8, k8, v8, qs, ks, vs, False, 1.3, G=64)
+    out = pkg.attention_full_int8(q8.to(dev), k8.to(dev), v8.to(dev), qs.to(dev), ks.to(dev), vs.to(dev), False, 1.3)
+    pkg.check_status()
+    # outputs here reach |o| ~ 30 (v_scale ~ N(0,1) times int8 values), where one fp16 ulp is 0.03:
+    # the absolute bar is applied relative to the output range
+    scale = max(1.0, ref.float().abs().max().item())
+    _close(oracle, out.float() / scale, ref.float() / scale, tight=False)
+
+
+def test_strided_qkv_layout(pkg, dev):
+    """[B,N,H,D] storage viewed as [B,H,N,D] (the layout of the reference's CUDA path) needs no copy."""
+    B, H, N, D = 2, 4, 256, 128
+    g = torch.Generator().manual_seed(6)
+    mk = lambda: torch.randint(-127, 128, (B, N, H, D), dtype=torch.int8, generator=g).to(dev)
+    q, k, v = mk(), mk(), mk()
+    qs = torch.rand(B, H, N, generator=g).to(dev) * 0.02
+    ks = torch.rand(B, H, N, generator=g).to(dev) * 0.02
+    vs = torch.rand(B, H, D, generator=g).to(dev) * 0.02
+    a = pkg.attention_full_int8(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3), qs, ks, vs, True, 0.1)
+    b = pkg.attention_full_int8(q.permute(0, 2, 1, 3).contiguous(), k.permute(0, 2, 1, 3).contiguous(),
+                                v.permute(0, 2, 1, 3).contiguous(), qs, ks, vs, True, 0.1)
+    pkg.check_status()
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("variant", ["full", "half"])
+def test_carried_state_equals_single_pass(variant, pkg, oracle, dev):
+    """KV fed in chunks through (m,l,acc) with global offsets == one pass, bit for bit; LSE matches the oracle."""
+    B, H, N, D, G = 1, 2, 512, 128, 128
+    q, k, v = make_qkv(44, B, H, N, D, std=0.5)
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    v8, vs = oracle.quant_perchannel(v)
+    vv = (v8 if variant == "full" else v).to(dev)
+    q8d, k8d, qsd, ksd, vsd = q8.to(dev), k8.to(dev), qs.to(dev).float(), ks.to(dev).float(), vs.to(dev).float()
+    fn = (lambda *a, **kw: pkg.attention_full_int8(a[0], a[1], a[2], a[3], a[4], vsd, True, 0.09, G=G, **kw)) \
+        if variant == "full" else (lambda *a, **kw: pkg.attention_int8(a[0], a[1], a[2], a[3], a[4], True, 0.09, G=G, **kw))
+    one, lse = fn(q8d, k8d, vv, qsd, ksd, return_lse=True)
+    st = None
+    for c in range(0, N, 256):
+        last = c + 256 >= N
+        res = fn(q8d, k8d[:, :, c:c + 256], vv[:, :, c:c + 256], qsd, ksd[:, :, c:c + 256].contiguous(),
+                 state=st, kv_offset=c, return_state=not last, write_o=last)
+        st = None if last else res[1]
+    pkg.check_status()
+    assert torch.equal(res, one)
+    _, (m, l, _) = oracle.int8_attention(q8, k8, v8 if variant == "full" else v, qs, ks, vs, True, 0.09,
+                                         variant=variant, G=G, return_state=True)
+    assert (lse.cpu() - oracle.log2_lse(m, l)).abs().max() < 1e-3
+
+
+def test_rne_p_rounding_mode(pkg, oracle, dev):
+    q, k, v = make_qkv(45, 1, 2, 256, 128)
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    v8, vs = oracle.quant_perchannel(v)
+    ref = oracle.attention_full_int8(q8, k8, v8, qs, ks, vs, False, 0.09, G=128, p_round="rne")
+    out = pkg.attention_full_int8(q8.to(dev), k8.to(dev), v8.to(dev), qs.to(dev), ks.to(dev), vs.to(dev), False, 0.09,
+                                  p_round="rne")
+    pkg.check_status()
+    _close(oracle, out, ref)
+
+
+def test_prologue_plus_forward(pkg, oracle, dev):
+    """int_flash_attention = fused quantisation + forward, against the same pipeline on the CPU."""
+    B, H, N, D = 2, 2, 512, 128
+    q, k, v = make_qkv(46, B, H, N, D)
+    sm = D ** -0.5
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    v8, vs = oracle.quant_perchannel(v)
+    for variant, causal in (("full", False), ("half", True)):
+        ref = oracle.int8_attention(q8, k8, v8 if variant == "full" else v, qs, ks, vs, causal, sm, variant=variant, G=128)
+        out = pkg.int_flash_attention(q.to(dev), k.to(dev), v.to(dev), causal, sm, variant=variant)
+        pkg.check_status()
+        _close(oracle, out, ref)
+
+
+def test_unsupported_shapes_raise(pkg, dev):
+    q = torch.zeros(1, 1, 96, 128, dtype=torch.int8, device=dev)
+    s = torch.ones(1, 1, 96, device=dev)
+    with pytest.raises(pkg.IntfaError, match="multiple of 128"):
+        pkg.attention_full_int8(q, q, q, s, s, torch.ones(1, 1, device=dev), False, 1.0)
+    q = torch.zeros(1, 1, 128, 32, dtype=torch.int8, device=dev)
+    s = torch.ones(1, 1, 128, device=dev)
+    with pytest.raises(pkg.IntfaError, match="head_dim"):
+        pkg.attention_full_int8(q, q, q, s, s, torch.ones(1, 1, device=dev), False, 1.0)
+
+
+# ------------------------------------------------------------------------------- full-size workloads
+def _full_size(pkg, oracle, dev, B, H, N, D, variant, causal, seed, outlier, heads):
+    """Run the whole configuration on the GPU from fp16 inputs; check sampled (batch, head) slices
+    against the CPU oracle, that a second run is bit-identical (no pipeline race), and that permuting
+    the batch permutes the output (work items are independent)."""
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    q = torch.randn(B, H, N, D, device=dev, generator=gen, dtype=torch.float32).half()
+    k = torch.randn(B, H, N, D, device=dev, generator=gen, dtype=torch.float32).half()
+    v = torch.randn(B, H, N, D, device=dev, generator=gen, dtype=torch.float32).half()
+    if outlier:
+        q[..., 17] *= 20
+        k[..., 17] *= 20
+    sm = D ** -0.5
+    out = pkg.int_flash_attention(q, k, v, causal, sm, variant=variant)
+    again = pkg.int_flash_attention(q, k, v, causal, sm, variant=variant)
+    pkg.check_status()
+    assert torch.equal(out, again)
+    perm = torch.arange(B - 1, -1, -1, device=dev)
+    outp = pkg.int_flash_attention(q[perm].contiguous(), k[perm].contiguous(), v[perm].contiguous(), causal, sm, variant=variant)
+    assert torch.equal(outp, out[perm])
+    assert torch.isfinite(out.float()).all()
+    for (b, h) in heads:
+        qc, kc, vc = (t[b:b + 1, h:h + 1].cpu() for t in (q, k, v))
+        q8, qs = oracle.quant_pertoken(qc)
+        k8, ks = oracle.quant_pertoken(kc)
+        v8, vs = oracle.quant_perchannel(vc)
+        ref = oracle.int8_attention(q8, k8, v8 if variant == "full" else vc, qs, ks, vs, causal, sm, variant=variant, G=128)
+        _close(oracle, out[b:b + 1, h:h + 1], ref)
+
+
+def test_full_size_full_int8_noncausal(pkg, oracle, dev):
+    """BASELINE config 1: batch 4, heads 32, seq 8192, head_dim 128, non-causal."""
+    _full_size(pkg, oracle, dev, 4, 32, 8192, 128, "full", False, 1001, False, [(0, 0), (3, 31)])
+
+
+def test_full_size_half_int8_causal(pkg, oracle, dev):
+    """BASELINE config 2: batch 8, heads 32, seq 4096, head_dim 128, causal, outlier channel."""
+    _full_size(pkg, oracle, dev, 8, 32, 4096, 128, "half", True, 1002, True, [(0, 0), (7, 13)])
+
+
+def test_status_word_clean(pkg, dev):
+    assert pkg.check_status(dev) == 0
