@@ -41,6 +41,13 @@ namespace intfa {
 constexpr int kBM = 128;          // query rows per work item
 constexpr int kThreads = 256;
 constexpr int kComputeThreads = 128;
+constexpr int kComputeRegs = 224;   // registers per softmax thread after setmaxnreg (service warps drop to 32)
+
+// The int32 accumulators in TMEM are pre-loaded with the bit pattern of the fp32 number 1.5*2^23.
+// The tensor core then leaves kMagicI + dot there, which READ AS FP32 is 1.5*2^23 + dot exactly
+// (|dot| <= 128*128*128 < 2^22), so one fp32 subtraction replaces an int->float conversion.
+constexpr uint32_t kMagicI = 0x4B400000u;
+constexpr float kMagicF = 12582912.0f;
 
 // device-side wait codes stored in *status (low byte = which wait, bits 8.. = blockIdx)
 enum WaitCode {
@@ -173,8 +180,23 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t sP = smem_u32(smem + C::OFF_P);
   const uint32_t sKS = smem_u32(smem + C::OFF_KS);
 
+  // arm the accumulators (see kMagicI): each softmax thread fills its own TMEM lane
+  if (warp >= 4) {
+    const uint32_t lane_sel0 = (uint32_t)((warp & 3) * 32) << 16;
+#pragma unroll
+    for (int cc = 0; cc < G / 32; ++cc) tmem_fill32(tS + lane_sel0 + cc * 32, kMagicI);
+    if constexpr (FULL) {
+#pragma unroll
+      for (int cc = 0; cc < D / 32; ++cc) tmem_fill32(tO + lane_sel0 + cc * 32, kMagicI);
+    }
+    tmem_st_wait();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+
   if (warp < 4) {
-    reg_dealloc<40>();
+    reg_dealloc<32>();
     if (warp == 0 && lane == 0) {
       // ------------------------------------------------------------------ TMA producer
       prefetch_tmap(&tmQ);
@@ -224,7 +246,7 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int kk = 0; kk < D / 32; ++kk) {
           const uint64_t ad = make_smem_desc(sQ + kk * 32, 16, C::SBO_QK, C::SWZ_QK);
           const uint64_t bd = make_smem_desc(sK + s * C::K_BYTES + kk * 32, 16, C::SBO_QK, C::SWZ_QK);
-          umma_i8(tS, ad, bd, C::IDESC_QK, kk > 0);
+          umma_i8(tS, ad, bd, C::IDESC_QK, 1);      // onto the pre-loaded magic
         }
         umma_commit(BAR(B_SFULL));
         umma_commit(BAR(B_KEMPTY + s));
@@ -252,7 +274,7 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (int kk = 0; kk < G / 32; ++kk) {
               const uint64_t ad = make_smem_desc(sP + kk * 32, 16, C::SBO_P, C::SWZ_P);
               const uint64_t bd = make_smem_desc(sV + s * C::V_BYTES + kk * (32 * D), 16, C::SBO_V, C::SWZ_V);
-              umma_i8(tO, ad, bd, C::IDESC_PV, kk > 0);
+              umma_i8(tO, ad, bd, C::IDESC_PV, 1);      // onto the pre-loaded magic
             }
           } else {
 #pragma unroll
@@ -277,32 +299,43 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     __syncwarp();
   } else {
     // -------------------------------------------------------------------- softmax / correction / epilogue
-    reg_alloc<216>();
+    reg_alloc<kComputeRegs>();
     const int row = threadIdx.x - 128;                       // row of the query tile == TMEM lane
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
     float* vsd_s = reinterpret_cast<float*>(smem + C::OFF_VSD);
     uint8_t* sP_gen = smem + C::OFF_P;
+    const uint64_t NEG_MAGIC2 = f2_pack(-kMagicF, -kMagicF);
     uint32_t step_it = 0;
     bool ok = true;
+#ifdef INTFA_TIMING
+    long long tm[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tq;
+#define INTFA_T0() tq = clock64()
+#define INTFA_T(i) { const long long now_ = clock64(); tm[i] += now_ - tq; tq = now_; }
+#else
+#define INTFA_T0()
+#define INTFA_T(i)
+#endif
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
       const TileInfo t = decode_tile(p, tile, G);
       const long long rowg = (long long)t.bh * p.Nq + (long long)t.mb * kBM + row;   // row in [B*H*Nq)
       const long long grow = p.q_off + (long long)t.mb * kBM + row;                  // global position
       const float qs_r = p.qs[(long long)t.b * p.qs_sb + (long long)t.h * p.qs_sh + t.mb * kBM + row];
+      const uint64_t QS2 = f2_pack(qs_r, qs_r);
       float m_i = -INFINITY, l_i = 1.0f;
-      float acc[D];
+      uint64_t acc2[D / 2];                                  // fp32 accumulator row, two channels per register pair
       if (p.state_in) {
         m_i = p.st_m[rowg];
         l_i = p.st_l[rowg];
-        const float4* a4 = reinterpret_cast<const float4*>(p.st_acc + rowg * D);
+        const ulonglong2* a4 = reinterpret_cast<const ulonglong2*>(p.st_acc + rowg * D);
 #pragma unroll
         for (int i = 0; i < D / 4; ++i) {
-          const float4 v = a4[i];
-          acc[4 * i] = v.x; acc[4 * i + 1] = v.y; acc[4 * i + 2] = v.z; acc[4 * i + 3] = v.w;
+          const ulonglong2 v = a4[i];
+          acc2[2 * i] = v.x;
+          acc2[2 * i + 1] = v.y;
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < D; ++i) acc[i] = 0.f;
+        for (int i = 0; i < D / 2; ++i) acc2[i] = 0ull;
       }
       if constexpr (FULL) {
         named_bar_sync(1, kComputeThreads);       // previous work item done with vsd_s
@@ -314,17 +347,22 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int j = 0; ok && j < t.nsteps; ++j, ++step_it) {
         const uint32_t s = step_it % NS, ph = (step_it / NS) & 1;
         const float* ks_s = reinterpret_cast<const float*>(smem + C::OFF_KS + s * C::KS_BYTES);
+        INTFA_T0();
         ok = mbar_wait(BAR(B_VFULL + s), ph, abort_flag, p.status, code_hi | W_KS_FULL);
         if (!ok) break;
+        INTFA_T(0);
         ok = mbar_wait(BAR(B_SFULL), step_it & 1, abort_flag, p.status, code_hi | W_S_FULL);
         if (!ok) break;
         tc_fence_after();
+        INTFA_T(1);
         const long long gcol0 = p.kv_off + (long long)j * G;
         const bool masked = p.causal && (gcol0 + G - 1 > p.q_off + (long long)t.mb * kBM);
         const bool dbg_here = (p.dbg_s != nullptr) && t.work == p.dbg_tile && j == p.dbg_step;
         const float c = p.c;
 
-        // ---- pass 1: row maximum
+        // ---- pass 1: TMEM holds kMagicI + S32, i.e. the fp32 number 1.5*2^23 + S32.  Subtracting the
+        // magic gives fp32(S32) exactly; s = (fp32(S32)*s_q)*s_k goes back into the same TMEM columns
+        // (on the causal band: x0 = s*c + bias) and the row maximum is taken on the way.
         float mx = -INFINITY;
 #pragma unroll
         for (int cc = 0; cc < G / 32; ++cc) {
@@ -333,16 +371,17 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_ld_wait(r);
           if (dbg_here) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) p.dbg_s[row * G + cc * 32 + i] = (int)r[i];
+            for (int i = 0; i < 32; ++i) p.dbg_s[row * G + cc * 32 + i] = (int)(r[i] - kMagicI);
           }
-          const float4* k4 = reinterpret_cast<const float4*>(ks_s + cc * 32);
+          const ulonglong2* k2 = reinterpret_cast<const ulonglong2*>(ks_s + cc * 32);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const float4 kk = k4[i];
-            float s0 = (__int2float_rn((int)r[4 * i + 0]) * qs_r) * kk.x;
-            float s1 = (__int2float_rn((int)r[4 * i + 1]) * qs_r) * kk.y;
-            float s2 = (__int2float_rn((int)r[4 * i + 2]) * qs_r) * kk.z;
-            float s3 = (__int2float_rn((int)r[4 * i + 3]) * qs_r) * kk.w;
+            const ulonglong2 kk = k2[i];
+            uint64_t v01 = f2_mul(f2_mul(f2_add(f2_packu(r[4 * i + 0], r[4 * i + 1]), NEG_MAGIC2), QS2), kk.x);
+            uint64_t v23 = f2_mul(f2_mul(f2_add(f2_packu(r[4 * i + 2], r[4 * i + 3]), NEG_MAGIC2), QS2), kk.y);
+            float s0, s1, s2, s3;
+            f2_unpack(v01, s0, s1);
+            f2_unpack(v23, s2, s3);
             if (masked) {
               const long long gc = gcol0 + cc * 32 + 4 * i;
               s0 = fmaf(s0, c, (gc + 0 <= grow) ? 0.f : -1.0e6f);
@@ -350,61 +389,61 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               s2 = fmaf(s2, c, (gc + 2 <= grow) ? 0.f : -1.0e6f);
               s3 = fmaf(s3, c, (gc + 3 <= grow) ? 0.f : -1.0e6f);
             }
-            mx = fmaxf(mx, fmaxf(fmaxf(s0, s1), fmaxf(s2, s3)));
+            mx = max3(mx, s0, s1);
+            mx = max3(mx, s2, s3);
+            r[4 * i + 0] = __float_as_uint(s0);
+            r[4 * i + 1] = __float_as_uint(s1);
+            r[4 * i + 2] = __float_as_uint(s2);
+            r[4 * i + 3] = __float_as_uint(s3);
           }
+          tmem_st32(tS + lane_sel + cc * 32, r);
         }
+        tmem_st_wait();
+        INTFA_T(2);
         const float m_new = masked ? fmaxf(m_i, mx) : fmaxf(m_i, mx * c);
         const float alpha = ex2_approx(m_i - m_new);
+        // x = u*cm - m_new with one rounding: u = s, cm = c off the band; u = x0, cm = 1 on it
+        const float cm = masked ? 1.0f : c;
+        const uint64_t C2 = f2_pack(cm, cm), NEG_M2 = f2_pack(-m_new, -m_new);
 
-        // ---- pass 2: p = exp2(x), row sum, P -> shared memory
-        float lsum = 0.f;
+        // ---- pass 2: p = exp2(x), row sum of the un-quantised p, P -> shared memory
+        uint64_t lsum_a = 0ull, lsum_b = 0ull;
 #pragma unroll
         for (int cc = 0; cc < G / 32; ++cc) {
           uint32_t r[32];
           tmem_ld32(tS + lane_sel + cc * 32, r);
           tmem_ld_wait(r);
-          const float4* k4 = reinterpret_cast<const float4*>(ks_s + cc * 32);
           uint32_t pk[FULL ? 8 : 16];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const float4 kk = k4[i];
-            float s0 = (__int2float_rn((int)r[4 * i + 0]) * qs_r) * kk.x;
-            float s1 = (__int2float_rn((int)r[4 * i + 1]) * qs_r) * kk.y;
-            float s2 = (__int2float_rn((int)r[4 * i + 2]) * qs_r) * kk.z;
-            float s3 = (__int2float_rn((int)r[4 * i + 3]) * qs_r) * kk.w;
             float x0, x1, x2, x3;
-            if (masked) {
-              const long long gc = gcol0 + cc * 32 + 4 * i;
-              x0 = fmaf(s0, c, (gc + 0 <= grow) ? 0.f : -1.0e6f) - m_new;
-              x1 = fmaf(s1, c, (gc + 1 <= grow) ? 0.f : -1.0e6f) - m_new;
-              x2 = fmaf(s2, c, (gc + 2 <= grow) ? 0.f : -1.0e6f) - m_new;
-              x3 = fmaf(s3, c, (gc + 3 <= grow) ? 0.f : -1.0e6f) - m_new;
-            } else {
-              x0 = fmaf(s0, c, -m_new);
-              x1 = fmaf(s1, c, -m_new);
-              x2 = fmaf(s2, c, -m_new);
-              x3 = fmaf(s3, c, -m_new);
-            }
+            f2_unpack(f2_fma(f2_packu(r[4 * i + 0], r[4 * i + 1]), C2, NEG_M2), x0, x1);
+            f2_unpack(f2_fma(f2_packu(r[4 * i + 2], r[4 * i + 3]), C2, NEG_M2), x2, x3);
             const float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
-            lsum += (p0 + p1) + (p2 + p3);
+            lsum_a = f2_add(lsum_a, f2_pack(p0, p1));
+            lsum_b = f2_add(lsum_b, f2_pack(p2, p3));
             if constexpr (FULL) {
-              int q0, q1, q2, q3;
               if constexpr (PRNE) {
-                q0 = min(__float2int_rn(p0 * 127.f), 127);
-                q1 = min(__float2int_rn(p1 * 127.f), 127);
-                q2 = min(__float2int_rn(p2 * 127.f), 127);
-                q3 = min(__float2int_rn(p3 * 127.f), 127);
+                // fp32 p*127 rounded to nearest-even integer: adding 1.5*2^23 leaves it in the low mantissa bits
+                const uint64_t K127 = f2_pack(127.f, 127.f), MAG2 = f2_pack(kMagicF, kMagicF);
+                uint32_t u0, u1, u2, u3;
+                f2_unpacku(f2_add(f2_mul(f2_pack(p0, p1), K127), MAG2), u0, u1);
+                f2_unpacku(f2_add(f2_mul(f2_pack(p2, p3), K127), MAG2), u2, u3);
+                pk[i] = __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
               } else {
+                // fp16(p)*127 and +0.5 as two separately rounded fp16 operations, then truncation.
+                // floor(y) without a conversion instruction: t = y + 1024 is 1024 + round(y) exactly
+                // (fp16 spacing is 1 there); where round(y) > y one is taken off; the integer then sits
+                // in the low byte of each half of t.
                 const __half2 k127 = __float2half2_rn(127.f), khalf = __float2half2_rn(0.5f);
-                const __half2 h01 = __hadd2(__hmul2(__floats2half2_rn(p0, p1), k127), khalf);
-                const __half2 h23 = __hadd2(__hmul2(__floats2half2_rn(p2, p3), k127), khalf);
-                q0 = __half2int_rz(__low2half(h01));
-                q1 = __half2int_rz(__high2half(h01));
-                q2 = __half2int_rz(__low2half(h23));
-                q3 = __half2int_rz(__high2half(h23));
+                const __half2 k1024 = __float2half2_rn(1024.f);
+                const __half2 y01 = __hadd2_rn(__hmul2_rn(__floats2half2_rn(p0, p1), k127), khalf);
+                const __half2 y23 = __hadd2_rn(__hmul2_rn(__floats2half2_rn(p2, p3), k127), khalf);
+                const __half2 t01 = __hadd2_rn(y01, k1024), t23 = __hadd2_rn(y23, k1024);
+                const __half2 f01 = __hsub2(t01, __hgt2(__hsub2(t01, k1024), y01));
+                const __half2 f23 = __hsub2(t23, __hgt2(__hsub2(t23, k1024), y23));
+                pk[i] = __byte_perm(*reinterpret_cast<const uint32_t*>(&f01), *reinterpret_cast<const uint32_t*>(&f23), 0x6420);
               }
-              pk[i] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
-                      ((uint32_t)(q3 & 0xff) << 24);
             } else {
               const __half2 h01 = __floats2half2_rn(p0, p1);
               const __half2 h23 = __floats2half2_rn(p2, p3);
@@ -438,43 +477,69 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               for (int i = 0; i < 16; ++i) dp[i] = pk[i];
             }
           }
+          // this chunk of S is consumed: put the magic back for the next QK^T accumulation
+          tmem_fill32(tS + lane_sel + cc * 32, kMagicI);
         }
-        // P visible to the tensor core's shared-memory reads; S fully read
+        tmem_st_wait();
+        // P visible to the tensor core's shared-memory reads; S re-armed
         fence_proxy_async_smem();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(BAR(B_PFULL));
-        l_i = l_i * alpha + lsum;
+        INTFA_T(3);
+        {
+          float la, lb, lc, ld;
+          f2_unpack(lsum_a, la, lb);
+          f2_unpack(lsum_b, lc, ld);
+          l_i = l_i * alpha + ((la + lb) + (lc + ld));
+        }
         m_i = m_new;
 
-        // ---- correction: acc = acc*alpha + O_j * s_v/127
+        // ---- correction: acc = acc*alpha + O_j * s_v/127   (half: acc = acc*alpha + O_j)
         ok = mbar_wait(BAR(B_OFULL), step_it & 1, abort_flag, p.status, code_hi | W_O_FULL);
         if (!ok) break;
         tc_fence_after();
+        INTFA_T(4);
+        const bool rescale = !__all_sync(0xffffffffu, alpha == 1.0f);   // acc*1 == acc: skip it warp-wide
+        const uint64_t ALPHA2 = f2_pack(alpha, alpha);
 #pragma unroll
         for (int cc = 0; cc < D / 32; ++cc) {
           uint32_t r[32];
           tmem_ld32(tO + lane_sel + cc * 32, r);
           tmem_ld_wait(r);
           if constexpr (FULL) {
-            const float4* v4 = reinterpret_cast<const float4*>(vsd_s + cc * 32);
+            tmem_fill32(tO + lane_sel + cc * 32, kMagicI);
+            const ulonglong2* v2 = reinterpret_cast<const ulonglong2*>(vsd_s + cc * 32);
+            if (rescale) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float4 vv = v4[i];
-              acc[cc * 32 + 4 * i + 0] = fmaf(__int2float_rn((int)r[4 * i + 0]), vv.x, acc[cc * 32 + 4 * i + 0] * alpha);
-              acc[cc * 32 + 4 * i + 1] = fmaf(__int2float_rn((int)r[4 * i + 1]), vv.y, acc[cc * 32 + 4 * i + 1] * alpha);
-              acc[cc * 32 + 4 * i + 2] = fmaf(__int2float_rn((int)r[4 * i + 2]), vv.z, acc[cc * 32 + 4 * i + 2] * alpha);
-              acc[cc * 32 + 4 * i + 3] = fmaf(__int2float_rn((int)r[4 * i + 3]), vv.w, acc[cc * 32 + 4 * i + 3] * alpha);
+              for (int i = 0; i < 8; ++i) {
+                const ulonglong2 vv = v2[i];
+                acc2[cc * 16 + 2 * i] = f2_fma(f2_add(f2_packu(r[4 * i + 0], r[4 * i + 1]), NEG_MAGIC2), vv.x,
+                                               f2_mul(acc2[cc * 16 + 2 * i], ALPHA2));
+                acc2[cc * 16 + 2 * i + 1] = f2_fma(f2_add(f2_packu(r[4 * i + 2], r[4 * i + 3]), NEG_MAGIC2), vv.y,
+                                                   f2_mul(acc2[cc * 16 + 2 * i + 1], ALPHA2));
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const ulonglong2 vv = v2[i];
+                acc2[cc * 16 + 2 * i] =
+                    f2_fma(f2_add(f2_packu(r[4 * i + 0], r[4 * i + 1]), NEG_MAGIC2), vv.x, acc2[cc * 16 + 2 * i]);
+                acc2[cc * 16 + 2 * i + 1] =
+                    f2_fma(f2_add(f2_packu(r[4 * i + 2], r[4 * i + 3]), NEG_MAGIC2), vv.y, acc2[cc * 16 + 2 * i + 1]);
+              }
             }
           } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              acc[cc * 32 + i] = fmaf(acc[cc * 32 + i], alpha, __uint_as_float(r[i]));
+            for (int i = 0; i < 16; ++i)
+              acc2[cc * 16 + i] = f2_fma(acc2[cc * 16 + i], ALPHA2, f2_packu(r[2 * i], r[2 * i + 1]));
           }
         }
+        if constexpr (FULL) tmem_st_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(BAR(B_OEMPTY));
+        INTFA_T(5);
       }
       if (!ok) break;
 
@@ -482,9 +547,9 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (p.state_out) {
         p.st_m[rowg] = m_i;
         p.st_l[rowg] = l_i;
-        float4* a4 = reinterpret_cast<float4*>(p.st_acc + rowg * D);
+        ulonglong2* a4 = reinterpret_cast<ulonglong2*>(p.st_acc + rowg * D);
 #pragma unroll
-        for (int i = 0; i < D / 4; ++i) a4[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+        for (int i = 0; i < D / 4; ++i) a4[i] = make_ulonglong2(acc2[2 * i], acc2[2 * i + 1]);
       }
       if (p.write_o) {
         __half* orow = p.o + (long long)t.b * p.o_sb + (long long)t.h * p.o_sh + (long long)(t.mb * kBM + row) * p.o_sn;
@@ -493,7 +558,9 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const __half2 h = __floats2half2_rn(acc[8 * i + 2 * e] / l_i, acc[8 * i + 2 * e + 1] / l_i);
+            float a, b;
+            f2_unpack(acc2[4 * i + e], a, b);
+            const __half2 h = __floats2half2_rn(a / l_i, b / l_i);
             w[e] = *reinterpret_cast<const uint32_t*>(&h);
           }
           *reinterpret_cast<uint4*>(orow + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -501,6 +568,11 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (p.lse) p.lse[rowg] = m_i + log2f(l_i);
       }
     }
+#ifdef INTFA_TIMING
+    if (row == 0 && p.dbg_s != nullptr && p.dbg_tile == -2) {
+      for (int i = 0; i < 8; ++i) p.dbg_s[blockIdx.x * 8 + i] = (int)(tm[i] >> 4);
+    }
+#endif
   }
 
   // -------------------------------------------------------------------------- teardown
