@@ -32,6 +32,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "intfa_internal.h"
 #include "intfa_ptx.cuh"
@@ -41,7 +42,6 @@ namespace intfa {
 constexpr int kBM = 128;          // query rows per work item
 constexpr int kThreads = 256;
 constexpr int kComputeThreads = 128;
-constexpr int kComputeRegs = 224;   // registers per softmax thread after setmaxnreg (service warps drop to 32)
 
 // The int32 accumulators in TMEM are pre-loaded with the bit pattern of the fp32 number 1.5*2^23.
 // The tensor core then leaves kMagicI + dot there, which READ AS FP32 is 1.5*2^23 + dot exactly
@@ -78,9 +78,14 @@ struct Cfg {
   static constexpr int NUM_BARS = 6 + 4 * NS;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;   // +1024: manual alignment slack
-  static constexpr int TMEM_COLS = (G + D) <= 128 ? 128 : 256;
+  // TMEM columns.  full: one int32 region shared by S = Q K^T (G columns) and O_j = P V (D columns) --
+  // S is dead once P is written, O_j is dead once it is folded into the accumulator -- followed by the
+  // fp32 accumulator (D columns).  half: S (G columns), then the fp32 accumulator the second MMA adds into.
   static constexpr int COL_S = 0;
-  static constexpr int COL_O = (G + D) <= 128 ? 64 : 128;
+  static constexpr int COL_O = 0;
+  static constexpr int COL_ACC = FULL ? (G > D ? G : D) : G;
+  static constexpr int TMEM_USED = COL_ACC + D;
+  static constexpr int TMEM_COLS = TMEM_USED <= 128 ? 128 : 256;
   // swizzle span = bytes of one operand row
   static constexpr uint64_t SWZ_QK = (D == 128) ? kSwz128 : kSwz64;     // Q, K rows are D bytes
   static constexpr uint32_t SBO_QK = 8 * D;
@@ -124,6 +129,14 @@ __device__ __forceinline__ uint32_t swz_off(int row, int chunk) {
   return a ^ (((a >> 7) & MASK) << 4);
 }
 
+#ifdef INTFA_TIMING
+#define INTFA_T0() tq = clock64()
+#define INTFA_T(i) { const long long now_ = clock64(); tm[i] += now_ - tq; tq = now_; }
+#else
+#define INTFA_T0()
+#define INTFA_T(i)
+#endif
+
 template <int D, int G, bool FULL, bool PRNE>
 __global__ void __launch_bounds__(kThreads, 2)
 intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -139,8 +152,10 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   const uint32_t bar0 = smem_u32(bars);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  // barrier indices
-  constexpr int B_QFULL = 0, B_QEMPTY = 1, B_SFULL = 2, B_PFULL = 3, B_OFULL = 4, B_OEMPTY = 5;
+  // barrier indices.  B_RFREE: full = the shared S/O region is consumed and re-armed (once per KV step);
+  // half = the accumulator has been read out by the epilogue (once per work item).
+  // B_OFULL: full = O_j ready (once per KV step); half = last PV of the work item done (once per work item).
+  constexpr int B_QFULL = 0, B_QEMPTY = 1, B_SFULL = 2, B_PFULL = 3, B_OFULL = 4, B_RFREE = 5;
   constexpr int B_KFULL = 6, B_KEMPTY = 6 + NS, B_VFULL = 6 + 2 * NS, B_VEMPTY = 6 + 3 * NS;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 4);
@@ -151,7 +166,7 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(BAR(B_SFULL), 1);
     mbar_init(BAR(B_PFULL), 4);
     mbar_init(BAR(B_OFULL), 1);
-    mbar_init(BAR(B_OEMPTY), 4);
+    mbar_init(BAR(B_RFREE), 4);
     for (int s = 0; s < NS; ++s) {
       mbar_init(BAR(B_KFULL + s), 1);
       mbar_init(BAR(B_KEMPTY + s), 1);
@@ -172,6 +187,7 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base + C::COL_S;
   const uint32_t tO = tmem_base + C::COL_O;
+  const uint32_t tA = tmem_base + C::COL_ACC;
   const int code_hi = (int)(blockIdx.x << 8);
 
   const uint32_t sQ = smem_u32(smem + C::OFF_Q);
@@ -180,15 +196,11 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t sP = smem_u32(smem + C::OFF_P);
   const uint32_t sKS = smem_u32(smem + C::OFF_KS);
 
-  // arm the accumulators (see kMagicI): each softmax thread fills its own TMEM lane
+  // arm the int32 region for the first Q K^T (see kMagicI): each softmax thread fills its own TMEM lane
   if (warp >= 4) {
     const uint32_t lane_sel0 = (uint32_t)((warp & 3) * 32) << 16;
 #pragma unroll
     for (int cc = 0; cc < G / 32; ++cc) tmem_fill32(tS + lane_sel0 + cc * 32, kMagicI);
-    if constexpr (FULL) {
-#pragma unroll
-      for (int cc = 0; cc < D / 32; ++cc) tmem_fill32(tO + lane_sel0 + cc * 32, kMagicI);
-    }
     tmem_st_wait();
     tc_fence_before();
   }
@@ -196,7 +208,6 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after();
 
   if (warp < 4) {
-    reg_dealloc<32>();
     if (warp == 0 && lane == 0) {
       // ------------------------------------------------------------------ TMA producer
       prefetch_tmap(&tmQ);
@@ -234,9 +245,8 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     } else if (warp == 1 && lane == 0) {
       // ------------------------------------------------------------------ MMA issuer
-      uint32_t kv_it = 0;      // KV tiles whose QK has been issued
-      uint32_t step_it = 0;    // KV tiles whose PV has been issued
-      uint32_t tile_it = 0;
+      uint32_t kv_it = 0;      // KV steps issued so far (all work items)
+      uint32_t tile_it = 0;    // work items with at least one KV step
       bool ok = true;
       auto issue_qk = [&](uint32_t it) -> bool {
         const uint32_t s = it % NS, ph = (it / NS) & 1;
@@ -257,40 +267,59 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (t.nsteps == 0) continue;
         ok = mbar_wait(BAR(B_QFULL), tile_it & 1, abort_flag, p.status, code_hi | W_Q_FULL);
         if (!ok) break;
-        ok = issue_qk(kv_it++);
-        if (!ok) break;
-        if (t.nsteps == 1) umma_commit(BAR(B_QEMPTY));
-        for (int j = 0; j < t.nsteps; ++j, ++step_it) {
-          const uint32_t s = step_it % NS, ph = (step_it / NS) & 1;
-          ok = mbar_wait(BAR(B_PFULL), step_it & 1, abort_flag, p.status, code_hi | W_P_FULL);
-          if (!ok) break;
-          ok = mbar_wait(BAR(B_VFULL + s), ph, abort_flag, p.status, code_hi | W_V_FULL);
-          if (!ok) break;
-          ok = mbar_wait(BAR(B_OEMPTY), (step_it & 1) ^ 1, abort_flag, p.status, code_hi | W_O_EMPTY);
-          if (!ok) break;
-          tc_fence_after();
-          if constexpr (FULL) {
+        if constexpr (FULL) {
+          for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
+            const uint32_t s = kv_it % NS, ph = (kv_it / NS) & 1;
+            // the shared S/O region must have been folded into the accumulator and re-armed
+            ok = mbar_wait(BAR(B_RFREE), (kv_it & 1) ^ 1, abort_flag, p.status, code_hi | W_O_EMPTY);
+            if (!ok) break;
+            ok = issue_qk(kv_it);
+            if (!ok) break;
+            if (j + 1 == t.nsteps) umma_commit(BAR(B_QEMPTY));
+            ok = mbar_wait(BAR(B_PFULL), kv_it & 1, abort_flag, p.status, code_hi | W_P_FULL);
+            if (!ok) break;
+            ok = mbar_wait(BAR(B_VFULL + s), ph, abort_flag, p.status, code_hi | W_V_FULL);
+            if (!ok) break;
+            tc_fence_after();
 #pragma unroll
             for (int kk = 0; kk < G / 32; ++kk) {
               const uint64_t ad = make_smem_desc(sP + kk * 32, 16, C::SBO_P, C::SWZ_P);
               const uint64_t bd = make_smem_desc(sV + s * C::V_BYTES + kk * (32 * D), 16, C::SBO_V, C::SWZ_V);
-              umma_i8(tO, ad, bd, C::IDESC_PV, 1);      // onto the pre-loaded magic
+              umma_i8(tO, ad, bd, C::IDESC_PV, 1);      // onto the re-armed magic
             }
-          } else {
+            umma_commit(BAR(B_OFULL));
+            umma_commit(BAR(B_VEMPTY + s));
+          }
+        } else {
+          // the previous work item's accumulator must have been read out before PV overwrites it
+          ok = mbar_wait(BAR(B_RFREE), (tile_it & 1) ^ 1, abort_flag, p.status, code_hi | W_O_EMPTY);
+          if (!ok) break;
+          ok = issue_qk(kv_it);
+          if (!ok) break;
+          if (t.nsteps == 1) umma_commit(BAR(B_QEMPTY));
+          for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
+            const uint32_t s = kv_it % NS, ph = (kv_it / NS) & 1;
+            ok = mbar_wait(BAR(B_PFULL), kv_it & 1, abort_flag, p.status, code_hi | W_P_FULL);
+            if (!ok) break;
+            ok = mbar_wait(BAR(B_VFULL + s), ph, abort_flag, p.status, code_hi | W_V_FULL);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t keep = (j > 0 || p.state_in) ? 1u : 0u;     // first PV of a fresh work item overwrites
 #pragma unroll
             for (int kk = 0; kk < G / 16; ++kk) {
               const uint64_t ad =
                   make_smem_desc(sP + (kk >> 2) * (kBM * 128) + (kk & 3) * 32, 16, C::SBO_P, C::SWZ_P);
               const uint64_t bd = make_smem_desc(sV + s * C::V_BYTES + kk * 2048, G * 128, C::SBO_V, C::SWZ_V);
-              umma_f16(tO, ad, bd, C::IDESC_PV, kk > 0);
+              umma_f16(tA, ad, bd, C::IDESC_PV, kk > 0 ? 1u : keep);
             }
-          }
-          umma_commit(BAR(B_OFULL));
-          umma_commit(BAR(B_VEMPTY + s));
-          if (j + 1 < t.nsteps) {
-            ok = issue_qk(kv_it++);
-            if (!ok) break;
-            if (j + 2 == t.nsteps) umma_commit(BAR(B_QEMPTY));
+            umma_commit(BAR(B_VEMPTY + s));
+            if (j + 1 < t.nsteps) {
+              ok = issue_qk(kv_it + 1);
+              if (!ok) break;
+              if (j + 2 == t.nsteps) umma_commit(BAR(B_QEMPTY));
+            } else {
+              umma_commit(BAR(B_OFULL));
+            }
           }
         }
         ++tile_it;
@@ -299,21 +328,21 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     __syncwarp();
   } else {
     // -------------------------------------------------------------------- softmax / correction / epilogue
-    reg_alloc<kComputeRegs>();
     const int row = threadIdx.x - 128;                       // row of the query tile == TMEM lane
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
     float* vsd_s = reinterpret_cast<float*>(smem + C::OFF_VSD);
     uint8_t* sP_gen = smem + C::OFF_P;
     const uint64_t NEG_MAGIC2 = f2_pack(-kMagicF, -kMagicF);
-    uint32_t step_it = 0;
+    uint32_t step_it = 0, tile_it = 0;
     bool ok = true;
+#ifdef INTFA_STAGGER
+    if (blockIdx.x >= (gridDim.x >> 1)) {
+      const long long t_start = clock64();
+      while (clock64() - t_start < INTFA_STAGGER) {}
+    }
+#endif
 #ifdef INTFA_TIMING
     long long tm[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tq;
-#define INTFA_T0() tq = clock64()
-#define INTFA_T(i) { const long long now_ = clock64(); tm[i] += now_ - tq; tq = now_; }
-#else
-#define INTFA_T0()
-#define INTFA_T(i)
 #endif
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
       const TileInfo t = decode_tile(p, tile, G);
@@ -322,20 +351,31 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const float qs_r = p.qs[(long long)t.b * p.qs_sb + (long long)t.h * p.qs_sh + t.mb * kBM + row];
       const uint64_t QS2 = f2_pack(qs_r, qs_r);
       float m_i = -INFINITY, l_i = 1.0f;
-      uint64_t acc2[D / 2];                                  // fp32 accumulator row, two channels per register pair
+      // fp32 accumulator row lives in TMEM (columns COL_ACC..): start from zero or from the carried state.
+      // (half, fresh start: nothing to do -- the first P V of the work item overwrites it)
       if (p.state_in) {
         m_i = p.st_m[rowg];
         l_i = p.st_l[rowg];
-        const ulonglong2* a4 = reinterpret_cast<const ulonglong2*>(p.st_acc + rowg * D);
-#pragma unroll
-        for (int i = 0; i < D / 4; ++i) {
-          const ulonglong2 v = a4[i];
-          acc2[2 * i] = v.x;
-          acc2[2 * i + 1] = v.y;
+        if constexpr (!FULL) {
+          if (t.nsteps > 0 && tile_it > 0) {     // previous work item's last P V must not be in flight: it is not,
+          }                                      // its O_FULL was awaited by the epilogue below
         }
-      } else {
 #pragma unroll
-        for (int i = 0; i < D / 2; ++i) acc2[i] = 0ull;
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t r[32];
+          const uint4* a4 = reinterpret_cast<const uint4*>(p.st_acc + rowg * D + cc * 32);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint4 v = a4[i];
+            r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
+          }
+          tmem_st32(tA + lane_sel + cc * 32, r);
+        }
+        tmem_st_wait();
+      } else if (FULL || t.nsteps == 0) {
+#pragma unroll
+        for (int cc = 0; cc < D / 32; ++cc) tmem_fill32(tA + lane_sel + cc * 32, 0u);
+        tmem_st_wait();
       }
       if constexpr (FULL) {
         named_bar_sync(1, kComputeThreads);       // previous work item done with vsd_s
@@ -360,11 +400,13 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const bool dbg_here = (p.dbg_s != nullptr) && t.work == p.dbg_tile && j == p.dbg_step;
         const float c = p.c;
 
-        // ---- pass 1: TMEM holds kMagicI + S32, i.e. the fp32 number 1.5*2^23 + S32.  Subtracting the
+        // ---- pass A: TMEM holds kMagicI + S32, i.e. the fp32 number 1.5*2^23 + S32.  Subtracting the
         // magic gives fp32(S32) exactly; s = (fp32(S32)*s_q)*s_k goes back into the same TMEM columns
-        // (on the causal band: x0 = s*c + bias) and the row maximum is taken on the way.
-        float mx = -INFINITY;
-#pragma unroll
+        // (on the causal band: x0 = s*c + bias) and the row maximum is taken on the way.  The chunk
+        // loops are deliberately NOT unrolled: the whole KV step has to stay resident in the
+        // instruction cache while two CTAs per SM run different phases of it.
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll 1
         for (int cc = 0; cc < G / 32; ++cc) {
           uint32_t r[32];
           tmem_ld32(tS + lane_sel + cc * 32, r);
@@ -373,62 +415,93 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 32; ++i) p.dbg_s[row * G + cc * 32 + i] = (int)(r[i] - kMagicI);
           }
-          const ulonglong2* k2 = reinterpret_cast<const ulonglong2*>(ks_s + cc * 32);
+          const float4* k4 = reinterpret_cast<const float4*>(ks_s + cc * 32);
+          if (!masked) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const ulonglong2 kk = k2[i];
-            uint64_t v01 = f2_mul(f2_mul(f2_add(f2_packu(r[4 * i + 0], r[4 * i + 1]), NEG_MAGIC2), QS2), kk.x);
-            uint64_t v23 = f2_mul(f2_mul(f2_add(f2_packu(r[4 * i + 2], r[4 * i + 3]), NEG_MAGIC2), QS2), kk.y);
-            float s0, s1, s2, s3;
-            f2_unpack(v01, s0, s1);
-            f2_unpack(v23, s2, s3);
-            if (masked) {
-              const long long gc = gcol0 + cc * 32 + 4 * i;
-              s0 = fmaf(s0, c, (gc + 0 <= grow) ? 0.f : -1.0e6f);
-              s1 = fmaf(s1, c, (gc + 1 <= grow) ? 0.f : -1.0e6f);
-              s2 = fmaf(s2, c, (gc + 2 <= grow) ? 0.f : -1.0e6f);
-              s3 = fmaf(s3, c, (gc + 3 <= grow) ? 0.f : -1.0e6f);
+            for (int i = 0; i < 8; ++i) {
+              const float4 kk = k4[i];
+              const float s0 = ((__uint_as_float(r[4 * i + 0]) - kMagicF) * qs_r) * kk.x;
+              const float s1 = ((__uint_as_float(r[4 * i + 1]) - kMagicF) * qs_r) * kk.y;
+              const float s2 = ((__uint_as_float(r[4 * i + 2]) - kMagicF) * qs_r) * kk.z;
+              const float s3 = ((__uint_as_float(r[4 * i + 3]) - kMagicF) * qs_r) * kk.w;
+              if (i & 1) {
+                mx2 = max3(mx2, s0, s1);
+                mx3 = max3(mx3, s2, s3);
+              } else {
+                mx0 = max3(mx0, s0, s1);
+                mx1 = max3(mx1, s2, s3);
+              }
+              r[4 * i + 0] = __float_as_uint(s0);
+              r[4 * i + 1] = __float_as_uint(s1);
+              r[4 * i + 2] = __float_as_uint(s2);
+              r[4 * i + 3] = __float_as_uint(s3);
             }
-            mx = max3(mx, s0, s1);
-            mx = max3(mx, s2, s3);
-            r[4 * i + 0] = __float_as_uint(s0);
-            r[4 * i + 1] = __float_as_uint(s1);
-            r[4 * i + 2] = __float_as_uint(s2);
-            r[4 * i + 3] = __float_as_uint(s3);
+          } else {
+            const long long gc0 = gcol0 + cc * 32;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float sraw = ((__uint_as_float(r[i]) - kMagicF) * qs_r) * ks_s[cc * 32 + i];
+              const float x0 = fmaf(sraw, c, (gc0 + i <= grow) ? 0.f : -1.0e6f);
+              mx0 = fmaxf(mx0, x0);
+              r[i] = __float_as_uint(x0);
+            }
           }
           tmem_st32(tS + lane_sel + cc * 32, r);
         }
         tmem_st_wait();
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         INTFA_T(2);
         const float m_new = masked ? fmaxf(m_i, mx) : fmaxf(m_i, mx * c);
         const float alpha = ex2_approx(m_i - m_new);
         // x = u*cm - m_new with one rounding: u = s, cm = c off the band; u = x0, cm = 1 on it
         const float cm = masked ? 1.0f : c;
-        const uint64_t C2 = f2_pack(cm, cm), NEG_M2 = f2_pack(-m_new, -m_new);
+        const float neg_m = -m_new;
 
-        // ---- pass 2: p = exp2(x), row sum of the un-quantised p, P -> shared memory
-        uint64_t lsum_a = 0ull, lsum_b = 0ull;
+        // half: bring the accumulator to the new maximum before P V adds into it
+        if constexpr (!FULL) {
+          const bool have_acc = (j > 0) || p.state_in;
+          if (have_acc && !__all_sync(0xffffffffu, alpha == 1.0f)) {
+            const uint64_t ALPHA2 = f2_pack(alpha, alpha);
+#pragma unroll 1
+            for (int cc = 0; cc < D / 32; ++cc) {
+              uint32_t r[32];
+              tmem_ld32(tA + lane_sel + cc * 32, r);
+              tmem_ld_wait(r);
 #pragma unroll
+              for (int i = 0; i < 16; ++i) f2_unpacku(f2_mul(f2_packu(r[2 * i], r[2 * i + 1]), ALPHA2), r[2 * i], r[2 * i + 1]);
+              tmem_st32(tA + lane_sel + cc * 32, r);
+            }
+          }
+        }
+
+        // ---- pass B: p = exp2(x), row sum of the un-quantised p, P -> shared memory; each chunk of the
+        // region is re-armed with the magic as soon as it has been read (full: for O_j = P V; half: for
+        // the next Q K^T)
+        float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
+#pragma unroll 1
         for (int cc = 0; cc < G / 32; ++cc) {
           uint32_t r[32];
           tmem_ld32(tS + lane_sel + cc * 32, r);
           tmem_ld_wait(r);
+          tmem_fill32(tS + lane_sel + cc * 32, kMagicI);
           uint32_t pk[FULL ? 8 : 16];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            float x0, x1, x2, x3;
-            f2_unpack(f2_fma(f2_packu(r[4 * i + 0], r[4 * i + 1]), C2, NEG_M2), x0, x1);
-            f2_unpack(f2_fma(f2_packu(r[4 * i + 2], r[4 * i + 3]), C2, NEG_M2), x2, x3);
-            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
-            lsum_a = f2_add(lsum_a, f2_pack(p0, p1));
-            lsum_b = f2_add(lsum_b, f2_pack(p2, p3));
+            const float p0 = ex2_approx(fmaf(__uint_as_float(r[4 * i + 0]), cm, neg_m));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(r[4 * i + 1]), cm, neg_m));
+            const float p2 = ex2_approx(fmaf(__uint_as_float(r[4 * i + 2]), cm, neg_m));
+            const float p3 = ex2_approx(fmaf(__uint_as_float(r[4 * i + 3]), cm, neg_m));
+            ls0 += p0;
+            ls1 += p1;
+            ls2 += p2;
+            ls3 += p3;
             if constexpr (FULL) {
               if constexpr (PRNE) {
                 // fp32 p*127 rounded to nearest-even integer: adding 1.5*2^23 leaves it in the low mantissa bits
-                const uint64_t K127 = f2_pack(127.f, 127.f), MAG2 = f2_pack(kMagicF, kMagicF);
-                uint32_t u0, u1, u2, u3;
-                f2_unpacku(f2_add(f2_mul(f2_pack(p0, p1), K127), MAG2), u0, u1);
-                f2_unpacku(f2_add(f2_mul(f2_pack(p2, p3), K127), MAG2), u2, u3);
+                const uint32_t u0 = __float_as_uint(__fadd_rn(__fmul_rn(p0, 127.f), kMagicF));
+                const uint32_t u1 = __float_as_uint(__fadd_rn(__fmul_rn(p1, 127.f), kMagicF));
+                const uint32_t u2 = __float_as_uint(__fadd_rn(__fmul_rn(p2, 127.f), kMagicF));
+                const uint32_t u3 = __float_as_uint(__fadd_rn(__fmul_rn(p3, 127.f), kMagicF));
                 pk[i] = __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
               } else {
                 // fp16(p)*127 and +0.5 as two separately rounded fp16 operations, then truncation.
@@ -477,100 +550,114 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               for (int i = 0; i < 16; ++i) dp[i] = pk[i];
             }
           }
-          // this chunk of S is consumed: put the magic back for the next QK^T accumulation
-          tmem_fill32(tS + lane_sel + cc * 32, kMagicI);
+        }
+        if constexpr (FULL && (D > G)) {
+          // O_j is wider than S: arm the remaining columns too
+#pragma unroll
+          for (int cc = G / 32; cc < D / 32; ++cc) tmem_fill32(tS + lane_sel + cc * 32, kMagicI);
         }
         tmem_st_wait();
-        // P visible to the tensor core's shared-memory reads; S re-armed
+        // P visible to the tensor core's shared-memory reads; TMEM region re-armed / accumulator rescaled
         fence_proxy_async_smem();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(BAR(B_PFULL));
         INTFA_T(3);
-        {
-          float la, lb, lc, ld;
-          f2_unpack(lsum_a, la, lb);
-          f2_unpack(lsum_b, lc, ld);
-          l_i = l_i * alpha + ((la + lb) + (lc + ld));
-        }
+        l_i = l_i * alpha + ((ls0 + ls1) + (ls2 + ls3));
         m_i = m_new;
 
-        // ---- correction: acc = acc*alpha + O_j * s_v/127   (half: acc = acc*alpha + O_j)
-        ok = mbar_wait(BAR(B_OFULL), step_it & 1, abort_flag, p.status, code_hi | W_O_FULL);
-        if (!ok) break;
-        tc_fence_after();
-        INTFA_T(4);
-        const bool rescale = !__all_sync(0xffffffffu, alpha == 1.0f);   // acc*1 == acc: skip it warp-wide
-        const uint64_t ALPHA2 = f2_pack(alpha, alpha);
-#pragma unroll
-        for (int cc = 0; cc < D / 32; ++cc) {
-          uint32_t r[32];
-          tmem_ld32(tO + lane_sel + cc * 32, r);
-          tmem_ld_wait(r);
-          if constexpr (FULL) {
-            tmem_fill32(tO + lane_sel + cc * 32, kMagicI);
+        if constexpr (FULL) {
+          // ---- correction: acc = acc*alpha + fp32(O_j) * s_v/127, accumulator row in TMEM
+          ok = mbar_wait(BAR(B_OFULL), step_it & 1, abort_flag, p.status, code_hi | W_O_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          INTFA_T(4);
+          const bool rescale = !__all_sync(0xffffffffu, alpha == 1.0f);   // acc*1 == acc: skip it warp-wide
+          const uint64_t ALPHA2 = f2_pack(rescale ? alpha : 1.0f, rescale ? alpha : 1.0f);
+#pragma unroll 1
+          for (int cc = 0; cc < D / 32; ++cc) {
+            uint32_t r[32], a[32];
+            tmem_ld32(tO + lane_sel + cc * 32, r);
+            tmem_ld32(tA + lane_sel + cc * 32, a);
+            tmem_ld_wait(r);
+            tmem_ld_wait(a);
+            // O_j chunk is in registers: re-arm it for the next Q K^T (which only uses the first G columns)
+            if (cc < G / 32) tmem_fill32(tS + lane_sel + cc * 32, kMagicI);
             const ulonglong2* v2 = reinterpret_cast<const ulonglong2*>(vsd_s + cc * 32);
-            if (rescale) {
 #pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const ulonglong2 vv = v2[i];
-                acc2[cc * 16 + 2 * i] = f2_fma(f2_add(f2_packu(r[4 * i + 0], r[4 * i + 1]), NEG_MAGIC2), vv.x,
-                                               f2_mul(acc2[cc * 16 + 2 * i], ALPHA2));
-                acc2[cc * 16 + 2 * i + 1] = f2_fma(f2_add(f2_packu(r[4 * i + 2], r[4 * i + 3]), NEG_MAGIC2), vv.y,
-                                                   f2_mul(acc2[cc * 16 + 2 * i + 1], ALPHA2));
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const ulonglong2 vv = v2[i];
-                acc2[cc * 16 + 2 * i] =
-                    f2_fma(f2_add(f2_packu(r[4 * i + 0], r[4 * i + 1]), NEG_MAGIC2), vv.x, acc2[cc * 16 + 2 * i]);
-                acc2[cc * 16 + 2 * i + 1] =
-                    f2_fma(f2_add(f2_packu(r[4 * i + 2], r[4 * i + 3]), NEG_MAGIC2), vv.y, acc2[cc * 16 + 2 * i + 1]);
-              }
+            for (int i = 0; i < 8; ++i) {
+              const ulonglong2 vv = v2[i];
+              const uint64_t a01 = f2_fma(f2_add(f2_packu(r[4 * i + 0], r[4 * i + 1]), NEG_MAGIC2), vv.x,
+                                          f2_mul(f2_packu(a[4 * i + 0], a[4 * i + 1]), ALPHA2));
+              const uint64_t a23 = f2_fma(f2_add(f2_packu(r[4 * i + 2], r[4 * i + 3]), NEG_MAGIC2), vv.y,
+                                          f2_mul(f2_packu(a[4 * i + 2], a[4 * i + 3]), ALPHA2));
+              f2_unpacku(a01, a[4 * i + 0], a[4 * i + 1]);
+              f2_unpacku(a23, a[4 * i + 2], a[4 * i + 3]);
             }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              acc2[cc * 16 + i] = f2_fma(acc2[cc * 16 + i], ALPHA2, f2_packu(r[2 * i], r[2 * i + 1]));
+            tmem_st32(tA + lane_sel + cc * 32, a);
           }
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(BAR(B_RFREE));
+          INTFA_T(5);
         }
-        if constexpr (FULL) tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(BAR(B_OEMPTY));
-        INTFA_T(5);
       }
       if (!ok) break;
 
       // ---- epilogue
+      if constexpr (!FULL) {
+        if (t.nsteps > 0) {
+          ok = mbar_wait(BAR(B_OFULL), tile_it & 1, abort_flag, p.status, code_hi | W_O_FULL);
+          if (!ok) break;
+          tc_fence_after();
+        }
+      }
+      const float inv_dummy = 0.f;
+      (void)inv_dummy;
+      __half* orow = p.o + (long long)t.b * p.o_sb + (long long)t.h * p.o_sh + (long long)(t.mb * kBM + row) * p.o_sn;
+#pragma unroll
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t a[32];
+        tmem_ld32(tA + lane_sel + cc * 32, a);
+        tmem_ld_wait(a);
+        if (p.state_out) {
+          uint4* a4 = reinterpret_cast<uint4*>(p.st_acc + rowg * D + cc * 32);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) a4[i] = make_uint4(a[4 * i], a[4 * i + 1], a[4 * i + 2], a[4 * i + 3]);
+        }
+        if (p.write_o) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const __half2 h = __floats2half2_rn(__uint_as_float(a[8 * i + 2 * e]) / l_i,
+                                                  __uint_as_float(a[8 * i + 2 * e + 1]) / l_i);
+              w[e] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(orow + cc * 32 + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
       if (p.state_out) {
         p.st_m[rowg] = m_i;
         p.st_l[rowg] = l_i;
-        ulonglong2* a4 = reinterpret_cast<ulonglong2*>(p.st_acc + rowg * D);
-#pragma unroll
-        for (int i = 0; i < D / 4; ++i) a4[i] = make_ulonglong2(acc2[2 * i], acc2[2 * i + 1]);
       }
-      if (p.write_o) {
-        __half* orow = p.o + (long long)t.b * p.o_sb + (long long)t.h * p.o_sh + (long long)(t.mb * kBM + row) * p.o_sn;
-#pragma unroll
-        for (int i = 0; i < D / 8; ++i) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float a, b;
-            f2_unpack(acc2[4 * i + e], a, b);
-            const __half2 h = __floats2half2_rn(a / l_i, b / l_i);
-            w[e] = *reinterpret_cast<const uint32_t*>(&h);
-          }
-          *reinterpret_cast<uint4*>(orow + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
+      if (p.write_o && p.lse) p.lse[rowg] = m_i + log2f(l_i);
+      if constexpr (!FULL) {
+        if (t.nsteps > 0) {
+          // accumulator read out: the next work item's first P V may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(BAR(B_RFREE));
+          ++tile_it;
         }
-        if (p.lse) p.lse[rowg] = m_i + log2f(l_i);
       }
     }
 #ifdef INTFA_TIMING
-    if (row == 0 && p.dbg_s != nullptr && p.dbg_tile == -2) {
-      for (int i = 0; i < 8; ++i) p.dbg_s[blockIdx.x * 8 + i] = (int)(tm[i] >> 4);
+    if (lane == 0 && p.dbg_s != nullptr && p.dbg_tile == -2 && blockIdx.x < 64) {
+      for (int i = 0; i < 8; ++i) p.dbg_s[(blockIdx.x * 4 + (warp & 3)) * 8 + i] = (int)(tm[i] >> 4);
     }
 #endif
   }
@@ -650,6 +737,9 @@ static int launch(const IntfaFwdParams* a, const KParams& kp, cudaStream_t strea
   if (sms <= 0) return set_error(INTFA_ERR_CUDA, "cannot query SM count");
   const int ctas_per_sm = (C::SMEM_BYTES + 1024) * 2 <= 227 * 1024 ? 2 : 1;
   int grid = sms * ctas_per_sm;
+#ifdef INTFA_TIMING
+  if (getenv("INTFA_ONE_CTA_PER_SM")) grid = sms;
+#endif
   if (grid > kp.num_tiles) grid = kp.num_tiles;
   kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, kp);
   cudaError_t e = cudaGetLastError();
