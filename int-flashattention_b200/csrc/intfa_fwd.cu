@@ -40,8 +40,9 @@
 namespace intfa {
 
 constexpr int kBM = 128;          // query rows per work item
-constexpr int kThreads = 256;
-constexpr int kComputeThreads = 128;
+constexpr int kThreads = 384;          // 4 service warps + 8 softmax warps
+constexpr int kComputeThreads = 256;
+constexpr int kServiceRegs = 40, kComputeRegs = 96;   // setmaxnreg split of the 80 registers/thread at launch
 
 // The int32 accumulators in TMEM are pre-loaded with the bit pattern of the fp32 number 1.5*2^23.
 // The tensor core then leaves kMagicI + dot there, which READ AS FP32 is 1.5*2^23 + dot exactly
@@ -64,7 +65,7 @@ struct Cfg {
   static constexpr int KS_BYTES = G * 4;
   // stages: keep the CTA under ~104 KB so two CTAs share an SM where possible
   static constexpr int BUDGET = 104 * 1024;
-  static constexpr int FIXED = Q_BYTES + P_BYTES + 2048;
+  static constexpr int FIXED = Q_BYTES + P_BYTES + 6144;
   static constexpr int PER_STAGE = K_BYTES + V_BYTES + KS_BYTES;
   static constexpr int NS_RAW = (BUDGET - FIXED) / PER_STAGE;
   static constexpr int NS = NS_RAW < 2 ? 2 : (NS_RAW > 4 ? 4 : NS_RAW);
@@ -74,7 +75,8 @@ struct Cfg {
   static constexpr int OFF_P = OFF_V + NS * V_BYTES;
   static constexpr int OFF_KS = OFF_P + P_BYTES;
   static constexpr int OFF_VSD = OFF_KS + NS * KS_BYTES;
-  static constexpr int OFF_BAR = OFF_VSD + D * 4;
+  static constexpr int OFF_XCH = OFF_VSD + D * 4;             // half-row maxima / sums exchange: 2 x [2][128] float2 + [2][128] float
+  static constexpr int OFF_BAR = OFF_XCH + 5 * 256 * 4;
   static constexpr int NUM_BARS = 6 + 4 * NS;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;   // +1024: manual alignment slack
@@ -164,9 +166,9 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(BAR(B_QFULL), 1);
     mbar_init(BAR(B_QEMPTY), 1);
     mbar_init(BAR(B_SFULL), 1);
-    mbar_init(BAR(B_PFULL), 4);
+    mbar_init(BAR(B_PFULL), 8);
     mbar_init(BAR(B_OFULL), 1);
-    mbar_init(BAR(B_RFREE), 4);
+    mbar_init(BAR(B_RFREE), 8);
     for (int s = 0; s < NS; ++s) {
       mbar_init(BAR(B_KFULL + s), 1);
       mbar_init(BAR(B_KEMPTY + s), 1);
@@ -197,7 +199,7 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t sKS = smem_u32(smem + C::OFF_KS);
 
   // arm the int32 region for the first Q K^T (see kMagicI): each softmax thread fills its own TMEM lane
-  if (warp >= 4) {
+  if (warp >= 4 && warp < 8) {
     const uint32_t lane_sel0 = (uint32_t)((warp & 3) * 32) << 16;
 #pragma unroll
     for (int cc = 0; cc < G / 32; ++cc) tmem_fill32(tS + lane_sel0 + cc * 32, kMagicI);
@@ -208,6 +210,7 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after();
 
   if (warp < 4) {
+    reg_dealloc<kServiceRegs>();
     if (warp == 0 && lane == 0) {
       // ------------------------------------------------------------------ TMA producer
       prefetch_tmap(&tmQ);
@@ -328,19 +331,26 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     __syncwarp();
   } else {
     // -------------------------------------------------------------------- softmax / correction / epilogue
-    const int row = threadIdx.x - 128;                       // row of the query tile == TMEM lane
-    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    // Eight warps, TWO threads per query row: warps cw and cw+4 own the same 32 TMEM lanes (rows) and
+    // split every row in halves -- `half` takes KV columns [half*G/2, ..) of S / P and output
+    // channels [half*D/2, ..) of O_j and the accumulator.  Per KV step the two threads of a row
+    // exchange one number (their partial row maximum) through shared memory; the row sum is kept
+    // as two partial sums and joined in the epilogue.
+    reg_alloc<kComputeRegs>();
+    const int cw = warp - 4;                                 // 0..7
+    const int quarter = cw & 3;                              // TMEM lane quarter this warp may access
+    const int half = cw >> 2;
+    const int row = quarter * 32 + lane;                     // row of the query tile == TMEM lane
+    const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
+    constexpr int GH = G / 2, DH = D / 2;                    // columns / channels per thread
+    const int col0 = half * GH, ch0 = half * DH;
     float* vsd_s = reinterpret_cast<float*>(smem + C::OFF_VSD);
+    float* xch_s = reinterpret_cast<float*>(smem + C::OFF_XCH);      // [2 parities][2 halves][128 rows] float2, then the epilogue's floats
     uint8_t* sP_gen = smem + C::OFF_P;
     const uint64_t NEG_MAGIC2 = f2_pack(-kMagicF, -kMagicF);
+    const int pair_bar = 2 + quarter;                        // named barrier of the two warps sharing these rows
     uint32_t step_it = 0, tile_it = 0;
     bool ok = true;
-#ifdef INTFA_STAGGER
-    if (blockIdx.x >= (gridDim.x >> 1)) {
-      const long long t_start = clock64();
-      while (clock64() - t_start < INTFA_STAGGER) {}
-    }
-#endif
 #ifdef INTFA_TIMING
     long long tm[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tq;
 #endif
@@ -349,44 +359,43 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const long long rowg = (long long)t.bh * p.Nq + (long long)t.mb * kBM + row;   // row in [B*H*Nq)
       const long long grow = p.q_off + (long long)t.mb * kBM + row;                  // global position
       const float qs_r = p.qs[(long long)t.b * p.qs_sb + (long long)t.h * p.qs_sh + t.mb * kBM + row];
-      const uint64_t QS2 = f2_pack(qs_r, qs_r);
-      float m_i = -INFINITY, l_i = 1.0f;
+      float m_i = -INFINITY;
+      float l_i = 1.0f;                                      // full row sum, kept identical in both threads of the row
+      float ls_pend = 0.f, alpha_pend = 1.f;                 // this thread's half-row sum of the latest KV step, not yet
+      bool have_pend = false;                                // folded into l_i (it travels with the next exchange)
       // fp32 accumulator row lives in TMEM (columns COL_ACC..): start from zero or from the carried state.
-      // (half, fresh start: nothing to do -- the first P V of the work item overwrites it)
+      // (half-int8, fresh start: nothing to do -- the first P V of the work item overwrites it)
       if (p.state_in) {
         m_i = p.st_m[rowg];
         l_i = p.st_l[rowg];
-        if constexpr (!FULL) {
-          if (t.nsteps > 0 && tile_it > 0) {     // previous work item's last P V must not be in flight: it is not,
-          }                                      // its O_FULL was awaited by the epilogue below
-        }
 #pragma unroll
-        for (int cc = 0; cc < D / 32; ++cc) {
+        for (int cc = 0; cc < DH / 32; ++cc) {
           uint32_t r[32];
-          const uint4* a4 = reinterpret_cast<const uint4*>(p.st_acc + rowg * D + cc * 32);
+          const uint4* a4 = reinterpret_cast<const uint4*>(p.st_acc + rowg * D + ch0 + cc * 32);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const uint4 v = a4[i];
             r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
           }
-          tmem_st32(tA + lane_sel + cc * 32, r);
+          tmem_st32(tA + lane_sel + ch0 + cc * 32, r);
         }
         tmem_st_wait();
       } else if (FULL || t.nsteps == 0) {
 #pragma unroll
-        for (int cc = 0; cc < D / 32; ++cc) tmem_fill32(tA + lane_sel + cc * 32, 0u);
+        for (int cc = 0; cc < DH / 32; ++cc) tmem_fill32(tA + lane_sel + ch0 + cc * 32, 0u);
         tmem_st_wait();
       }
       if constexpr (FULL) {
         named_bar_sync(1, kComputeThreads);       // previous work item done with vsd_s
-        if (row < D)
-          vsd_s[row] = p.vs[(long long)t.b * p.vs_sb + (long long)t.h * p.vs_sh + (long long)row * p.vs_sd] / 127.0f;
+        const int ch = threadIdx.x - 128;
+        if (ch < D)
+          vsd_s[ch] = p.vs[(long long)t.b * p.vs_sb + (long long)t.h * p.vs_sh + (long long)ch * p.vs_sd] / 127.0f;
         named_bar_sync(1, kComputeThreads);
       }
 
       for (int j = 0; ok && j < t.nsteps; ++j, ++step_it) {
         const uint32_t s = step_it % NS, ph = (step_it / NS) & 1;
-        const float* ks_s = reinterpret_cast<const float*>(smem + C::OFF_KS + s * C::KS_BYTES);
+        const float* ks_s = reinterpret_cast<const float*>(smem + C::OFF_KS + s * C::KS_BYTES) + col0;
         INTFA_T0();
         ok = mbar_wait(BAR(B_VFULL + s), ph, abort_flag, p.status, code_hi | W_KS_FULL);
         if (!ok) break;
@@ -399,21 +408,22 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const bool masked = p.causal && (gcol0 + G - 1 > p.q_off + (long long)t.mb * kBM);
         const bool dbg_here = (p.dbg_s != nullptr) && t.work == p.dbg_tile && j == p.dbg_step;
         const float c = p.c;
+        const uint32_t tSh = tS + lane_sel + col0;           // this thread's S columns
 
         // ---- pass A: TMEM holds kMagicI + S32, i.e. the fp32 number 1.5*2^23 + S32.  Subtracting the
         // magic gives fp32(S32) exactly; s = (fp32(S32)*s_q)*s_k goes back into the same TMEM columns
         // (on the causal band: x0 = s*c + bias) and the row maximum is taken on the way.  The chunk
         // loops are deliberately NOT unrolled: the whole KV step has to stay resident in the
-        // instruction cache while two CTAs per SM run different phases of it.
+        // instruction cache while the CTAs of an SM run different phases of it.
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll 1
-        for (int cc = 0; cc < G / 32; ++cc) {
+        for (int cc = 0; cc < GH / 32; ++cc) {
           uint32_t r[32];
-          tmem_ld32(tS + lane_sel + cc * 32, r);
+          tmem_ld32(tSh + cc * 32, r);
           tmem_ld_wait(r);
           if (dbg_here) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) p.dbg_s[row * G + cc * 32 + i] = (int)(r[i] - kMagicI);
+            for (int i = 0; i < 32; ++i) p.dbg_s[row * G + col0 + cc * 32 + i] = (int)(r[i] - kMagicI);
           }
           const float4* k4 = reinterpret_cast<const float4*>(ks_s + cc * 32);
           if (!masked) {
@@ -437,7 +447,7 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               r[4 * i + 3] = __float_as_uint(s3);
             }
           } else {
-            const long long gc0 = gcol0 + cc * 32;
+            const long long gc0 = gcol0 + col0 + cc * 32;
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const float sraw = ((__uint_as_float(r[i]) - kMagicF) * qs_r) * ks_s[cc * 32 + i];
@@ -446,10 +456,20 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               r[i] = __float_as_uint(x0);
             }
           }
-          tmem_st32(tS + lane_sel + cc * 32, r);
+          tmem_st32(tSh + cc * 32, r);
+        }
+        // join the two half-row maxima; the previous step's half-row sums ride along, so that the row
+        // sum is formed as l = l*alpha + (sum_half0 + sum_half1) in both threads, step by step
+        float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        {
+          float2* x = reinterpret_cast<float2*>(xch_s) + (step_it & 1) * 256;
+          x[half * 128 + row] = make_float2(mx, ls_pend);
+          named_bar_sync(pair_bar, 64);
+          const float2 e0 = x[row], e1 = x[128 + row];
+          mx = fmaxf(e0.x, e1.x);
+          if (have_pend) l_i = l_i * alpha_pend + (e0.y + e1.y);
         }
         tmem_st_wait();
-        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         INTFA_T(2);
         const float m_new = masked ? fmaxf(m_i, mx) : fmaxf(m_i, mx * c);
         const float alpha = ex2_approx(m_i - m_new);
@@ -457,33 +477,33 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const float cm = masked ? 1.0f : c;
         const float neg_m = -m_new;
 
-        // half: bring the accumulator to the new maximum before P V adds into it
+        // half-int8: bring the accumulator to the new maximum before P V adds into it
         if constexpr (!FULL) {
           const bool have_acc = (j > 0) || p.state_in;
           if (have_acc && !__all_sync(0xffffffffu, alpha == 1.0f)) {
             const uint64_t ALPHA2 = f2_pack(alpha, alpha);
 #pragma unroll 1
-            for (int cc = 0; cc < D / 32; ++cc) {
+            for (int cc = 0; cc < DH / 32; ++cc) {
               uint32_t r[32];
-              tmem_ld32(tA + lane_sel + cc * 32, r);
+              tmem_ld32(tA + lane_sel + ch0 + cc * 32, r);
               tmem_ld_wait(r);
 #pragma unroll
               for (int i = 0; i < 16; ++i) f2_unpacku(f2_mul(f2_packu(r[2 * i], r[2 * i + 1]), ALPHA2), r[2 * i], r[2 * i + 1]);
-              tmem_st32(tA + lane_sel + cc * 32, r);
+              tmem_st32(tA + lane_sel + ch0 + cc * 32, r);
             }
           }
         }
 
         // ---- pass B: p = exp2(x), row sum of the un-quantised p, P -> shared memory; each chunk of the
-        // region is re-armed with the magic as soon as it has been read (full: for O_j = P V; half: for
-        // the next Q K^T)
+        // region is re-armed with the magic as soon as it has been read (full-int8: for O_j = P V;
+        // half-int8: for the next Q K^T)
         float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
 #pragma unroll 1
-        for (int cc = 0; cc < G / 32; ++cc) {
+        for (int cc = 0; cc < GH / 32; ++cc) {
           uint32_t r[32];
-          tmem_ld32(tS + lane_sel + cc * 32, r);
+          tmem_ld32(tSh + cc * 32, r);
           tmem_ld_wait(r);
-          tmem_fill32(tS + lane_sel + cc * 32, kMagicI);
+          tmem_fill32(tSh + cc * 32, kMagicI);
           uint32_t pk[FULL ? 8 : 16];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -524,15 +544,16 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               pk[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&h23);
             }
           }
+          const int colb = col0 + cc * 32;                   // first column of this chunk within the KV tile
           if constexpr (FULL) {
             // 32 int8 = two 16-byte chunks of this row
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-              const uint32_t off = swz_off<G>(row, cc * 2 + h);
+              const uint32_t off = swz_off<G>(row, (colb >> 4) + h);
               *reinterpret_cast<uint4*>(sP_gen + off) = make_uint4(pk[4 * h], pk[4 * h + 1], pk[4 * h + 2], pk[4 * h + 3]);
             }
             if (dbg_here && p.dbg_p) {
-              uint32_t* dp = reinterpret_cast<uint32_t*>(reinterpret_cast<int8_t*>(p.dbg_p) + row * G + cc * 32);
+              uint32_t* dp = reinterpret_cast<uint32_t*>(reinterpret_cast<int8_t*>(p.dbg_p) + row * G + colb);
 #pragma unroll
               for (int i = 0; i < 8; ++i) dp[i] = pk[i];
             }
@@ -540,21 +561,21 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             // 32 fp16 = four 16-byte chunks; columns [64*blk, 64*blk+64) live in block blk of 128 rows x 128 B
 #pragma unroll
             for (int h = 0; h < 4; ++h) {
-              const int col = cc * 32 + h * 8;
+              const int col = colb + h * 8;
               const uint32_t off = (col >> 6) * (kBM * 128) + swz_off<128>(row, (col & 63) >> 3);
               *reinterpret_cast<uint4*>(sP_gen + off) = make_uint4(pk[4 * h], pk[4 * h + 1], pk[4 * h + 2], pk[4 * h + 3]);
             }
             if (dbg_here && p.dbg_p) {
-              uint32_t* dp = reinterpret_cast<uint32_t*>(reinterpret_cast<__half*>(p.dbg_p) + row * G + cc * 32);
+              uint32_t* dp = reinterpret_cast<uint32_t*>(reinterpret_cast<__half*>(p.dbg_p) + row * G + colb);
 #pragma unroll
               for (int i = 0; i < 16; ++i) dp[i] = pk[i];
             }
           }
         }
         if constexpr (FULL && (D > G)) {
-          // O_j is wider than S: arm the remaining columns too
+          // O_j is wider than S: arm the columns S did not cover (split between the two threads of the row)
 #pragma unroll
-          for (int cc = G / 32; cc < D / 32; ++cc) tmem_fill32(tS + lane_sel + cc * 32, kMagicI);
+          for (int cc = 0; cc < (D - G) / 64; ++cc) tmem_fill32(tS + lane_sel + G + half * ((D - G) / 2) + cc * 32, kMagicI);
         }
         tmem_st_wait();
         // P visible to the tensor core's shared-memory reads; TMEM region re-armed / accumulator rescaled
@@ -563,7 +584,9 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(BAR(B_PFULL));
         INTFA_T(3);
-        l_i = l_i * alpha + ((ls0 + ls1) + (ls2 + ls3));
+        ls_pend = (ls0 + ls1) + (ls2 + ls3);
+        alpha_pend = alpha;
+        have_pend = true;
         m_i = m_new;
 
         if constexpr (FULL) {
@@ -575,17 +598,16 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           const bool rescale = !__all_sync(0xffffffffu, alpha == 1.0f);   // acc*1 == acc: skip it warp-wide
           const uint64_t ALPHA2 = f2_pack(rescale ? alpha : 1.0f, rescale ? alpha : 1.0f);
 #pragma unroll 1
-          for (int cc = 0; cc < D / 32; ++cc) {
-            uint32_t r[32], a[32];
-            tmem_ld32(tO + lane_sel + cc * 32, r);
-            tmem_ld32(tA + lane_sel + cc * 32, a);
-            tmem_ld_wait(r);
-            tmem_ld_wait(a);
-            // O_j chunk is in registers: re-arm it for the next Q K^T (which only uses the first G columns)
-            if (cc < G / 32) tmem_fill32(tS + lane_sel + cc * 32, kMagicI);
-            const ulonglong2* v2 = reinterpret_cast<const ulonglong2*>(vsd_s + cc * 32);
+          for (int cc = 0; cc < DH / 16; ++cc) {
+            uint32_t r[16], a[16];
+            const int chb = ch0 + cc * 16;
+            tmem_ld16(tO + lane_sel + chb, r);
+            tmem_ld16(tA + lane_sel + chb, a);
+            tmem_ld_wait16(r);
+            tmem_ld_wait16(a);
+            const ulonglong2* v2 = reinterpret_cast<const ulonglong2*>(vsd_s + chb);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < 4; ++i) {
               const ulonglong2 vv = v2[i];
               const uint64_t a01 = f2_fma(f2_add(f2_packu(r[4 * i + 0], r[4 * i + 1]), NEG_MAGIC2), vv.x,
                                           f2_mul(f2_packu(a[4 * i + 0], a[4 * i + 1]), ALPHA2));
@@ -594,8 +616,13 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               f2_unpacku(a01, a[4 * i + 0], a[4 * i + 1]);
               f2_unpacku(a23, a[4 * i + 2], a[4 * i + 3]);
             }
-            tmem_st32(tA + lane_sel + cc * 32, a);
+            tmem_st16(tA + lane_sel + chb, a);
           }
+          // O_j is folded in: re-arm the columns this thread has just read that the next Q K^T will
+          // accumulate into (the first G of the region)
+#pragma unroll
+          for (int cc = 0; cc < DH / 32; ++cc)
+            if (ch0 + cc * 32 < G) tmem_fill32(tS + lane_sel + ch0 + cc * 32, kMagicI);
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
@@ -613,16 +640,23 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tc_fence_after();
         }
       }
-      const float inv_dummy = 0.f;
-      (void)inv_dummy;
-      __half* orow = p.o + (long long)t.b * p.o_sb + (long long)t.h * p.o_sh + (long long)(t.mb * kBM + row) * p.o_sn;
+      // fold in the last KV step's half-row sums
+      float l_row = l_i;
+      if (have_pend) {
+        float* x = xch_s + 1024;                             // [2 halves][128 rows], epilogue only
+        named_bar_sync(pair_bar, 64);                        // partner done reading the previous work item's sums
+        x[half * 128 + row] = ls_pend;
+        named_bar_sync(pair_bar, 64);
+        l_row = l_i * alpha_pend + (x[row] + x[128 + row]);
+      }
+      __half* orow = p.o + (long long)t.b * p.o_sb + (long long)t.h * p.o_sh + (long long)(t.mb * kBM + row) * p.o_sn + ch0;
 #pragma unroll
-      for (int cc = 0; cc < D / 32; ++cc) {
+      for (int cc = 0; cc < DH / 32; ++cc) {
         uint32_t a[32];
-        tmem_ld32(tA + lane_sel + cc * 32, a);
+        tmem_ld32(tA + lane_sel + ch0 + cc * 32, a);
         tmem_ld_wait(a);
         if (p.state_out) {
-          uint4* a4 = reinterpret_cast<uint4*>(p.st_acc + rowg * D + cc * 32);
+          uint4* a4 = reinterpret_cast<uint4*>(p.st_acc + rowg * D + ch0 + cc * 32);
 #pragma unroll
           for (int i = 0; i < 8; ++i) a4[i] = make_uint4(a[4 * i], a[4 * i + 1], a[4 * i + 2], a[4 * i + 3]);
         }
@@ -632,19 +666,21 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             uint32_t w[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const __half2 h = __floats2half2_rn(__uint_as_float(a[8 * i + 2 * e]) / l_i,
-                                                  __uint_as_float(a[8 * i + 2 * e + 1]) / l_i);
+              const __half2 h = __floats2half2_rn(__uint_as_float(a[8 * i + 2 * e]) / l_row,
+                                                  __uint_as_float(a[8 * i + 2 * e + 1]) / l_row);
               w[e] = *reinterpret_cast<const uint32_t*>(&h);
             }
             *reinterpret_cast<uint4*>(orow + cc * 32 + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
       }
-      if (p.state_out) {
-        p.st_m[rowg] = m_i;
-        p.st_l[rowg] = l_i;
+      if (half == 0) {
+        if (p.state_out) {
+          p.st_m[rowg] = m_i;
+          p.st_l[rowg] = l_row;
+        }
+        if (p.write_o && p.lse) p.lse[rowg] = m_i + log2f(l_row);
       }
-      if (p.write_o && p.lse) p.lse[rowg] = m_i + log2f(l_i);
       if constexpr (!FULL) {
         if (t.nsteps > 0) {
           // accumulator read out: the next work item's first P V may overwrite it
@@ -656,8 +692,8 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
 #ifdef INTFA_TIMING
-    if (lane == 0 && p.dbg_s != nullptr && p.dbg_tile == -2 && blockIdx.x < 64) {
-      for (int i = 0; i < 8; ++i) p.dbg_s[(blockIdx.x * 4 + (warp & 3)) * 8 + i] = (int)(tm[i] >> 4);
+    if (lane == 0 && p.dbg_s != nullptr && p.dbg_tile == -2 && blockIdx.x < 64 && half == 0) {
+      for (int i = 0; i < 8; ++i) p.dbg_s[(blockIdx.x * 4 + quarter) * 8 + i] = (int)(tm[i] >> 4);
     }
 #endif
   }
