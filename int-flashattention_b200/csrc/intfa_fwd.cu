@@ -42,6 +42,13 @@ namespace intfa {
 constexpr int kBM = 128;          // query rows per work item
 constexpr int kThreads = 384;          // 4 service warps + 8 softmax warps
 constexpr int kComputeThreads = 256;
+#ifndef INTFA_SLEEP_P
+#define INTFA_SLEEP_P 200
+#define INTFA_SLEEP_W 40
+#define INTFA_SLEEP_M 20
+#endif
+constexpr int kSleepProducer = INTFA_SLEEP_P, kSleepWatcher = INTFA_SLEEP_W, kSleepMma = INTFA_SLEEP_M;   // ns between polls
+constexpr int kBarS = 6, kBarO = 7;   // named barriers the watcher warp releases the softmax warps on
 constexpr int kServiceRegs = 40, kComputeRegs = 96;   // setmaxnreg split of the 80 registers/thread at launch
 
 // The int32 accumulators in TMEM are pre-loaded with the bit pattern of the fp32 number 1.5*2^23.
@@ -221,18 +228,18 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
         const TileInfo t = decode_tile(p, tile, G);
         if (t.nsteps == 0) continue;
-        ok = mbar_wait(BAR(B_QEMPTY), (tile_it & 1) ^ 1, abort_flag, p.status, code_hi | W_Q_EMPTY);
+        ok = mbar_wait<kSleepProducer>(BAR(B_QEMPTY), (tile_it & 1) ^ 1, abort_flag, p.status, code_hi | W_Q_EMPTY);
         if (!ok) break;
         mbar_expect_tx(BAR(B_QFULL), C::Q_BYTES);
         tma_load_4d(sQ, &tmQ, BAR(B_QFULL), 0, t.mb * kBM, t.h, t.b);
         const float* ks_row = p.ks + (long long)t.b * p.ks_sb + (long long)t.h * p.ks_sh;
         for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
           const uint32_t s = kv_it % NS, ph = (kv_it / NS) & 1;
-          ok = mbar_wait(BAR(B_KEMPTY + s), ph ^ 1, abort_flag, p.status, code_hi | W_K_EMPTY);
+          ok = mbar_wait<kSleepProducer>(BAR(B_KEMPTY + s), ph ^ 1, abort_flag, p.status, code_hi | W_K_EMPTY);
           if (!ok) break;
           mbar_expect_tx(BAR(B_KFULL + s), C::K_BYTES);
           tma_load_4d(sK + s * C::K_BYTES, &tmK, BAR(B_KFULL + s), 0, j * G, t.h, t.b);
-          ok = mbar_wait(BAR(B_VEMPTY + s), ph ^ 1, abort_flag, p.status, code_hi | W_V_EMPTY);
+          ok = mbar_wait<kSleepProducer>(BAR(B_VEMPTY + s), ph ^ 1, abort_flag, p.status, code_hi | W_V_EMPTY);
           if (!ok) break;
           mbar_expect_tx(BAR(B_VFULL + s), C::V_BYTES + C::KS_BYTES);
           if constexpr (FULL) {
@@ -274,12 +281,12 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
             const uint32_t s = kv_it % NS, ph = (kv_it / NS) & 1;
             // the shared S/O region must have been folded into the accumulator and re-armed
-            ok = mbar_wait(BAR(B_RFREE), (kv_it & 1) ^ 1, abort_flag, p.status, code_hi | W_O_EMPTY);
+            ok = mbar_wait<kSleepMma>(BAR(B_RFREE), (kv_it & 1) ^ 1, abort_flag, p.status, code_hi | W_O_EMPTY);
             if (!ok) break;
             ok = issue_qk(kv_it);
             if (!ok) break;
             if (j + 1 == t.nsteps) umma_commit(BAR(B_QEMPTY));
-            ok = mbar_wait(BAR(B_PFULL), kv_it & 1, abort_flag, p.status, code_hi | W_P_FULL);
+            ok = mbar_wait<kSleepMma>(BAR(B_PFULL), kv_it & 1, abort_flag, p.status, code_hi | W_P_FULL);
             if (!ok) break;
             ok = mbar_wait(BAR(B_VFULL + s), ph, abort_flag, p.status, code_hi | W_V_FULL);
             if (!ok) break;
@@ -295,14 +302,14 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         } else {
           // the previous work item's accumulator must have been read out before PV overwrites it
-          ok = mbar_wait(BAR(B_RFREE), (tile_it & 1) ^ 1, abort_flag, p.status, code_hi | W_O_EMPTY);
+          ok = mbar_wait<kSleepMma>(BAR(B_RFREE), (tile_it & 1) ^ 1, abort_flag, p.status, code_hi | W_O_EMPTY);
           if (!ok) break;
           ok = issue_qk(kv_it);
           if (!ok) break;
           if (t.nsteps == 1) umma_commit(BAR(B_QEMPTY));
           for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
             const uint32_t s = kv_it % NS, ph = (kv_it / NS) & 1;
-            ok = mbar_wait(BAR(B_PFULL), kv_it & 1, abort_flag, p.status, code_hi | W_P_FULL);
+            ok = mbar_wait<kSleepMma>(BAR(B_PFULL), kv_it & 1, abort_flag, p.status, code_hi | W_P_FULL);
             if (!ok) break;
             ok = mbar_wait(BAR(B_VFULL + s), ph, abort_flag, p.status, code_hi | W_V_FULL);
             if (!ok) break;
@@ -324,6 +331,29 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               umma_commit(BAR(B_OFULL));
             }
           }
+        }
+        ++tile_it;
+      }
+    } else if (warp == 3) {
+      // ------------------------------------------------------------------ watcher
+      // Turns the tensor core's mbarrier completions into named-barrier releases: the eight softmax
+      // warps block in bar.sync (no issue slots) instead of polling; this one warp polls for them.
+      uint32_t kv_it = 0, tile_it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        const TileInfo t = decode_tile(p, tile, G);
+        if (t.nsteps == 0) continue;
+        for (int j = 0; ok && j < t.nsteps; ++j, ++kv_it) {
+          ok = mbar_wait<kSleepWatcher>(BAR(B_SFULL), kv_it & 1, abort_flag, p.status, code_hi | W_S_FULL);
+          named_bar_arrive(kBarS, kComputeThreads + 32);
+          if constexpr (FULL) {
+            if (ok) ok = mbar_wait<kSleepWatcher>(BAR(B_OFULL), kv_it & 1, abort_flag, p.status, code_hi | W_O_FULL);
+            named_bar_arrive(kBarO, kComputeThreads + 32);
+          }
+        }
+        if constexpr (!FULL) {
+          if (ok) ok = mbar_wait<kSleepWatcher>(BAR(B_OFULL), tile_it & 1, abort_flag, p.status, code_hi | W_O_FULL);
+          named_bar_arrive(kBarO, kComputeThreads + 32);
         }
         ++tile_it;
       }
@@ -400,7 +430,8 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         ok = mbar_wait(BAR(B_VFULL + s), ph, abort_flag, p.status, code_hi | W_KS_FULL);
         if (!ok) break;
         INTFA_T(0);
-        ok = mbar_wait(BAR(B_SFULL), step_it & 1, abort_flag, p.status, code_hi | W_S_FULL);
+        named_bar_sync(kBarS, kComputeThreads + 32);          // S = Q K^T is in TMEM (released by the watcher warp)
+        ok = (*abort_flag == 0);
         if (!ok) break;
         tc_fence_after();
         INTFA_T(1);
@@ -419,8 +450,14 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll 1
         for (int cc = 0; cc < GH / 32; ++cc) {
           uint32_t r[32];
+#ifdef INTFA_TIMING
+          const long long tl0 = clock64();
+#endif
           tmem_ld32(tSh + cc * 32, r);
           tmem_ld_wait(r);
+#ifdef INTFA_TIMING
+          tm[6] += clock64() - tl0;
+#endif
           if (dbg_here) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) p.dbg_s[row * G + col0 + cc * 32 + i] = (int)(r[i] - kMagicI);
@@ -501,8 +538,14 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll 1
         for (int cc = 0; cc < GH / 32; ++cc) {
           uint32_t r[32];
+#ifdef INTFA_TIMING
+          const long long tl0 = clock64();
+#endif
           tmem_ld32(tSh + cc * 32, r);
           tmem_ld_wait(r);
+#ifdef INTFA_TIMING
+          tm[7] += clock64() - tl0;
+#endif
           tmem_fill32(tSh + cc * 32, kMagicI);
           uint32_t pk[FULL ? 8 : 16];
 #pragma unroll
@@ -591,12 +634,12 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
         if constexpr (FULL) {
           // ---- correction: acc = acc*alpha + fp32(O_j) * s_v/127, accumulator row in TMEM
-          ok = mbar_wait(BAR(B_OFULL), step_it & 1, abort_flag, p.status, code_hi | W_O_FULL);
+          named_bar_sync(kBarO, kComputeThreads + 32);        // O_j = P V is in TMEM
+          ok = (*abort_flag == 0);
           if (!ok) break;
           tc_fence_after();
           INTFA_T(4);
-          const bool rescale = !__all_sync(0xffffffffu, alpha == 1.0f);   // acc*1 == acc: skip it warp-wide
-          const uint64_t ALPHA2 = f2_pack(rescale ? alpha : 1.0f, rescale ? alpha : 1.0f);
+          const uint64_t ALPHA2 = f2_pack(alpha, alpha);
 #pragma unroll 1
           for (int cc = 0; cc < DH / 16; ++cc) {
             uint32_t r[16], a[16];
@@ -635,7 +678,8 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // ---- epilogue
       if constexpr (!FULL) {
         if (t.nsteps > 0) {
-          ok = mbar_wait(BAR(B_OFULL), tile_it & 1, abort_flag, p.status, code_hi | W_O_FULL);
+          named_bar_sync(kBarO, kComputeThreads + 32);        // last P V of the work item is in the accumulator
+          ok = (*abort_flag == 0);
           if (!ok) break;
           tc_fence_after();
         }

@@ -42,24 +42,51 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return done;
 }
+// try_wait that lets the hardware park the thread for up to `ns` nanoseconds (it is woken when the
+// phase completes), so a waiting warp does not burn issue slots in a poll loop
+__device__ __forceinline__ uint32_t mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.b32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(done)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return done;
+}
 
 // Bounded wait.  Every spin in the kernels goes through here: after `kWaitLimitCycles`
 // SM cycles without completion the waiter records `code` in *status (first writer wins),
 // raises the CTA-wide abort flag and returns false; every other waiter of the CTA sees
 // the flag on its next poll and returns false as well, so the CTA drains and exits.
 constexpr long long kWaitLimitCycles = 1LL << 31;   // about one second at B200 clocks
+constexpr uint32_t kParkNs = 20000;                 // longest single park; bounds how late an abort is seen
 
+// The abort flag and the clock are looked at every 64th poll only: the poll loop itself stays a
+// handful of instructions.
+// kSleepNs > 0: sleep that long between polls, so that a polling service warp leaves the issue
+// slots of its scheduler to the warps that compute.
+template <int kSleepNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
+  long long t0 = 0;
+  uint32_t polls = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
-      *abort_flag = 1;
-      if (status) atomicCAS(status, 0, code);
-      return false;
+    if (kSleepNs > 0) __nanosleep(kSleepNs);
+    if (mbar_try_wait_parked(bar, parity, kParkNs)) return true;
+    if ((++polls & 63u) == 0u) {
+      if (*abort_flag) return false;
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, code);
+        return false;
+      }
     }
   }
 }
@@ -315,6 +342,10 @@ __device__ __forceinline__ void reg_dealloc() {
 }
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+// non-blocking arrival on a named barrier that other warps block on with named_bar_sync
+__device__ __forceinline__ void named_bar_arrive(int id, int nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
 }  // namespace intfa
