@@ -5,6 +5,8 @@
 //   amax  = max |x|                       (exact in fp16)
 //   scale = fp16( fp32(amax) / 127 )      (IEEE fp32 division, then round-to-nearest fp16)
 //   q     = int8( rint( fp16( fp32(x) / fp32(scale) ) ) )   (rint = half-to-even, as torch.round)
+// The per-element division is evaluated as a correctly rounded quotient from one reciprocal per
+// row/channel and two fmas (see quant_byte), so it costs no division instruction per element.
 // Scales are written as fp32 holding the fp16-representable value.  amax == 0 gives
 // scale 0 and q 0 (the reference computes 0/0 there).
 //
@@ -23,26 +25,50 @@ namespace intfa {
 __device__ __forceinline__ float scale_from_amax(float amax) {
   return __half2float(__float2half_rn(__fdiv_rn(amax, 127.0f)));
 }
-__device__ __forceinline__ int quant_one(float x, float s) {
-  if (s == 0.f) return 0;
-  const float t = __half2float(__float2half_rn(__fdiv_rn(x, s)));
-  return (int)rintf(t);
+// Correctly rounded x / s without a division per element (Markstein): with r = RN(1/s),
+// q0 = RN(x*r), e = x - q0*s (exact in one fma), q = RN(q0 + e*r) equals RN(x/s) unless the
+// significand of s is all ones -- impossible here because s is an fp16 value held in fp32.
+// Then the reference's rounding chain: fp16(q), and rint() done by adding 1.5*2^23, which also
+// leaves the two's-complement integer in the low byte of the sum.
+__device__ __forceinline__ uint32_t quant_byte(float x, float s, float r) {
+  const float q0 = x * r;
+  const float e = fmaf(-q0, s, x);
+  const float q = fmaf(e, r, q0);
+  const float t = __half2float(__float2half_rn(q));
+  const uint32_t u = __float_as_uint(t + 12582912.0f);
+  return s == 0.f ? 0u : (u & 0xffu);
 }
 __device__ __forceinline__ float amax8(const uint4& v) {
   const __half2* h = reinterpret_cast<const __half2*>(&v);
   __half2 m = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
   return fmaxf(__low2float(m), __high2float(m));
 }
-__device__ __forceinline__ uint2 quant8(const uint4& v, const float* s) {
-  const __half* h = reinterpret_cast<const __half*>(&v);
+// s[i], r[i] = scale and its correctly rounded reciprocal for element i of the 8
+__device__ __forceinline__ uint2 quant8(const uint4& v, const float* s, const float* r) {
+  const __half2* h2 = reinterpret_cast<const __half2*>(&v);
   uint32_t w[2] = {0u, 0u};
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int q = quant_one(__half2float(h[i]), s[i]);
-    w[i >> 2] |= (uint32_t)(q & 0xff) << (8 * (i & 3));
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(h2[i]);
+    w[i >> 1] |= quant_byte(f.x, s[2 * i], r[2 * i]) << (16 * (i & 1));
+    w[i >> 1] |= quant_byte(f.y, s[2 * i + 1], r[2 * i + 1]) << (16 * (i & 1) + 8);
   }
   return make_uint2(w[0], w[1]);
 }
+
+// streaming 128-bit load / 64-bit store: the tensors are touched once, keep them out of L1
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream(void* p, uint2 v) {
+  asm volatile("st.global.cs.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+
+constexpr int kQuantUnroll = 4;    // independent 128-bit loads in flight per lane
 
 template <int D>
 __global__ void __launch_bounds__(256) quant_pertoken_kernel(const __half* __restrict__ x, long long sB, long long sH,
@@ -50,29 +76,39 @@ __global__ void __launch_bounds__(256) quant_pertoken_kernel(const __half* __res
                                                              float* __restrict__ scale, int H, int N,
                                                              long long total_rows) {
   constexpr int LPR = D / 8;         // lanes per row
-  constexpr int RPW = 32 / LPR;      // rows per warp
+  constexpr int RPW = 32 / LPR;      // rows per warp and load
   const int lane = threadIdx.x & 31;
   const int sub = lane % LPR;
   const long long warp_g = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
-  for (long long row0 = warp_g * RPW; row0 < total_rows; row0 += nwarps * RPW) {
-    const long long row = row0 + lane / LPR;
-    const bool live = row < total_rows;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (live) {
-      const long long bh = row / N;
-      const int n = (int)(row - bh * N);
-      const int b = (int)(bh / H), h = (int)(bh - (long long)b * H);
-      v = *reinterpret_cast<const uint4*>(x + b * sB + h * sH + n * sN + sub * 8);
-    }
-    float a = amax8(v);
+  for (long long row0 = warp_g * (RPW * kQuantUnroll); row0 < total_rows; row0 += nwarps * (RPW * kQuantUnroll)) {
+    uint4 v[kQuantUnroll];
+    long long rows[kQuantUnroll];
 #pragma unroll
-    for (int o = LPR / 2; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-    const float s = scale_from_amax(a);
-    if (live) {
-      const float sv[8] = {s, s, s, s, s, s, s, s};
-      *reinterpret_cast<uint2*>(x8 + row * D + sub * 8) = quant8(v, sv);
-      if (sub == 0) scale[row] = s;
+    for (int u = 0; u < kQuantUnroll; ++u) {
+      const long long row = row0 + u * RPW + lane / LPR;
+      rows[u] = row;
+      v[u] = make_uint4(0, 0, 0, 0);
+      if (row < total_rows) {
+        const long long bh = row / N;
+        const int n = (int)(row - bh * N);
+        const int b = (int)(bh / H), h = (int)(bh - (long long)b * H);
+        v[u] = ld_stream(x + b * sB + h * sH + n * sN + sub * 8);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kQuantUnroll; ++u) {
+      float a = amax8(v[u]);
+#pragma unroll
+      for (int o = LPR / 2; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+      const float s = scale_from_amax(a);
+      if (rows[u] < total_rows) {
+        const float rcp = __frcp_rn(s);
+        const float sv[8] = {s, s, s, s, s, s, s, s};
+        const float rv[8] = {rcp, rcp, rcp, rcp, rcp, rcp, rcp, rcp};
+        st_stream(x8 + rows[u] * D + sub * 8, quant8(v[u], sv, rv));
+        if (sub == 0) scale[rows[u]] = s;
+      }
     }
   }
 }
@@ -95,11 +131,19 @@ __global__ void __launch_bounds__(256) v_colmax_kernel(const __half* __restrict_
   __half2 m[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) m[i] = __float2half2_rn(0.f);
-  for (int r = r_begin + warp * RPW + lane / LPR; r < r_end; r += nw * RPW) {
-    const uint4 v = *reinterpret_cast<const uint4*>(base + r * sN);
-    const __half2* hv = reinterpret_cast<const __half2*>(&v);
+  for (int r0 = r_begin + warp * RPW + lane / LPR; r0 < r_end; r0 += nw * RPW * kQuantUnroll) {
+    uint4 v[kQuantUnroll];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) m[i] = __hmax2(m[i], __habs2(hv[i]));
+    for (int u = 0; u < kQuantUnroll; ++u) {
+      const int r = r0 + u * nw * RPW;
+      v[u] = r < r_end ? *reinterpret_cast<const uint4*>(base + r * sN) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < kQuantUnroll; ++u) {
+      const __half2* hv = reinterpret_cast<const __half2*>(&v[u]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) m[i] = __hmax2(m[i], __habs2(hv[i]));
+    }
   }
   float f[8];
 #pragma unroll
@@ -156,16 +200,28 @@ __global__ void __launch_bounds__(256) v_quant_kernel(const __half* __restrict__
       scale[bh] = s_scale[0];
     }
   }
-  float sv[8];
+  float sv[8], rv[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) sv[i] = s_scale[sub * 8 + i];
+  for (int i = 0; i < 8; ++i) {
+    sv[i] = s_scale[sub * 8 + i];
+    rv[i] = __frcp_rn(sv[i]);
+  }
   const __half* base = x + b * sB + h * sH + sub * 8;
   int8_t* obase = x8 + (long long)bh * N * D + sub * 8;
   const int r_begin = blockIdx.x * rows_per_cta;
   const int r_end = min(N, r_begin + rows_per_cta);
-  for (int r = r_begin + warp * RPW + lane / LPR; r < r_end; r += nw * RPW) {
-    const uint4 v = *reinterpret_cast<const uint4*>(base + r * sN);
-    *reinterpret_cast<uint2*>(obase + (long long)r * D) = quant8(v, sv);
+  for (int r0 = r_begin + warp * RPW + lane / LPR; r0 < r_end; r0 += nw * RPW * kQuantUnroll) {
+    uint4 v[kQuantUnroll];
+#pragma unroll
+    for (int u = 0; u < kQuantUnroll; ++u) {
+      const int r = r0 + u * nw * RPW;
+      v[u] = r < r_end ? ld_stream(base + r * sN) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < kQuantUnroll; ++u) {
+      const int r = r0 + u * nw * RPW;
+      if (r < r_end) st_stream(obase + (long long)r * D, quant8(v[u], sv, rv));
+    }
   }
 }
 
@@ -185,7 +241,7 @@ int quant_pertoken(const void* x, const int64_t* st, void* x8, float* scale, int
   const long long rows = (long long)B * H * N;
   const int sms = sm_count_cached();
   if (sms <= 0) return set_error(INTFA_ERR_CUDA, "cannot query SM count");
-  const int rpw = 32 / (D / 8);
+  const int rpw = 32 / (D / 8) * kQuantUnroll;
   long long want = (rows + 8LL * rpw - 1) / (8LL * rpw);          // CTAs of 8 warps, one row group each
   const int grid = (int)(want < (long long)sms * 8 ? (want < 1 ? 1 : want) : (long long)sms * 8);
   if (D == 128)
