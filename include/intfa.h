@@ -130,6 +130,32 @@ int intfa_v_quant_from_colmax(const void* v, const int64_t v_stride[3], const vo
                               void* v8, float* scale, int32_t mode,
                               int32_t B, int32_t H, int32_t N, int32_t D, void* stream);
 
+/*
+ * intfa_quant_v for callers that cannot allocate device memory.
+ * No counterpart in the reference (its quantisers are PyTorch expressions that allocate freely).
+ *
+ * Some hosts of this library -- a plug-in running inside another runtime's memory pool, a callback
+ * on a serving thread that may not call cudaMalloc, code between the capture points of a larger
+ * pipeline -- have nowhere to get the B*H*D-word scratch that intfa_quant_v asks for.  This variant
+ * takes the same inputs and outputs and no workspace: the column-absmax scratch is a fixed array
+ * inside the library image (256 KiB on every GPU that loads the library, held until the process
+ * exits).  It calls no cudaMalloc/cudaFree and no allocating library routine.
+ *
+ *  - Limit: B*H*D <= intfa_quant_v_static_max_words() (65536); larger shapes get INTFA_ERR_TOO_LARGE
+ *    and should use intfa_quant_v.
+ *  - The first call on each device looks the array's device address up (cudaGetSymbolAddress with
+ *    that device current) and remembers it; make that first call before any stream capture begins.
+ *  - All calls on a device share the one array.  Each call clears the part it uses (the array keeps
+ *    the previous call's maxima), so calls issued one after another on a stream are fine, but two
+ *    calls that can overlap on the GPU (different streams, no dependency) race on it and must be
+ *    serialised by the caller.
+ * Results are bit-identical to intfa_quant_v.
+ */
+int intfa_quant_v_static(const void* v, const int64_t v_stride[3],
+                         void* v8, float* scale, int32_t mode,
+                         int32_t B, int32_t H, int32_t N, int32_t D, void* stream);
+size_t intfa_quant_v_static_max_words(void);
+
 /* Widens fp16 scales (as benchmark.py produces them) to the fp32 the kernel reads
  * (promotion done in-kernel by the reference, flash_atten_full_int8.py:37-38). n elements. */
 int intfa_scales_f16_to_f32(const void* src_f16, float* dst_f32, int64_t n, void* stream);

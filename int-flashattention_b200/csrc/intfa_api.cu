@@ -161,6 +161,18 @@ int intfa_v_quant_from_colmax(const void* v, const int64_t v_stride[3], const vo
   return v_quant_from_colmax(v, v_stride, colmax, v8, scale, mode, B, H, N, D, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int intfa_quant_v_static(const void* v, const int64_t v_stride[3], void* v8, float* scale, int32_t mode, int32_t B,
+                         int32_t H, int32_t N, int32_t D, void* stream) {
+  int rc = check_quant_args(v, v_stride, v8, scale, B, H, N, D);
+  if (rc) return rc;
+  if (mode != INTFA_VSCALE_PER_TENSOR && mode != INTFA_VSCALE_PER_CHANNEL)
+    return set_error(INTFA_ERR_INVALID_ARG, "mode must be INTFA_VSCALE_PER_TENSOR or INTFA_VSCALE_PER_CHANNEL");
+  if ((long long)B * H > 65535) return set_error(INTFA_ERR_TOO_LARGE, "B*H=%lld exceeds 65535", (long long)B * H);
+  return quant_v_static(v, v_stride, v8, scale, mode, B, H, N, D, reinterpret_cast<cudaStream_t>(stream));
+}
+
+size_t intfa_quant_v_static_max_words(void) { return (size_t)kStaticColmaxWords; }
+
 int intfa_scales_f16_to_f32(const void* src_f16, float* dst_f32, int64_t n, void* stream) {
   if (n < 0 || (n > 0 && (!src_f16 || !dst_f32))) return set_error(INTFA_ERR_INVALID_ARG, "bad argument");
   return scales_f16_to_f32(src_f16, dst_f32, n, reinterpret_cast<cudaStream_t>(stream));

@@ -38,6 +38,9 @@ int quant_v(const void* v, const int64_t* st, void* v8, float* scale, int mode, 
 int v_colmax(const void* v, const int64_t* st, void* colmax, int B, int H, int N, int D, cudaStream_t stream);
 int v_quant_from_colmax(const void* v, const int64_t* st, const void* colmax, void* v8, float* scale, int mode, int B,
                         int H, int N, int D, cudaStream_t stream);
+constexpr int kStaticColmaxWords = 65536;   // 256 KiB: built-in scratch of intfa_quant_v_static (B*H*D limit)
+int quant_v_static(const void* v, const int64_t* st, void* v8, float* scale, int mode, int B, int H, int N, int D,
+                   cudaStream_t stream);
 int scales_f16_to_f32(const void* src, float* dst, long long n, cudaStream_t stream);
 
 }  // namespace intfa

@@ -296,6 +296,55 @@ int quant_v(const void* v, const int64_t* st, void* v8, float* scale, int mode, 
   return v_quant_from_colmax(v, st, workspace, v8, scale, mode, B, H, N, D, stream);
 }
 
+// ---------------------------------------------------------------------------------------------
+// V quantisation for callers that must not allocate (intfa_quant_v_static)
+// ---------------------------------------------------------------------------------------------
+// Column-absmax scratch that lives in the library image instead of in a caller-provided buffer.
+// Every GPU that loads the library keeps these kStaticColmaxWords*4 bytes until the process exits.
+// In host code `g_static_colmax` is only a handle for the symbol, not a device address, so the
+// address is looked up once per device with cudaGetSymbolAddress and that pointer is what the
+// kernels are given.
+__device__ __align__(256) static unsigned int g_static_colmax[kStaticColmaxWords];
+
+static unsigned int* static_colmax_ptr(int* rc) {
+  static unsigned int* ptr[64];
+  static bool have[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    *rc = set_error(INTFA_ERR_CUDA, "cannot query the current device");
+    return nullptr;
+  }
+  if (!have[dev]) {
+    void* sym = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&sym, g_static_colmax);     // with device `dev` current
+    if (e != cudaSuccess || sym == nullptr) {
+      *rc = set_error(INTFA_ERR_CUDA, "cudaGetSymbolAddress(static colmax scratch): %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    ptr[dev] = static_cast<unsigned int*>(sym);
+    have[dev] = true;
+  }
+  *rc = INTFA_OK;
+  return ptr[dev];
+}
+
+int quant_v_static(const void* v, const int64_t* st, void* v8, float* scale, int mode, int B, int H, int N, int D,
+                   cudaStream_t stream) {
+  const long long words = (long long)B * H * D;
+  if (words > kStaticColmaxWords)
+    return set_error(INTFA_ERR_TOO_LARGE, "B*H*D = %lld exceeds the built-in scratch of %d words; use intfa_quant_v",
+                     words, kStaticColmaxWords);
+  int rc;
+  unsigned int* scratch = static_colmax_ptr(&rc);
+  if (!scratch) return rc;
+  // the scratch keeps the previous call's maxima: clear the part this call uses
+  cudaError_t e = cudaMemsetAsync(scratch, 0, (size_t)words * sizeof(unsigned int), stream);
+  if (e != cudaSuccess) return set_error(INTFA_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+  rc = v_colmax(v, st, scratch, B, H, N, D, stream);
+  if (rc) return rc;
+  return v_quant_from_colmax(v, st, scratch, v8, scale, mode, B, H, N, D, stream);
+}
+
 int scales_f16_to_f32(const void* src, float* dst, long long n, cudaStream_t stream) {
   if (n <= 0) return INTFA_OK;
   long long blocks = (n + 255) / 256;
