@@ -130,7 +130,7 @@ def synth(B, H, N, D, std, outlier, seed, device):
     return q.half(), k.half(), v.half()
 
 
-def cpu_reference_leg(workload, budget_s=20.0, max_heads=8):
+def cpu_reference_leg(workload, budget_s=15.0, max_heads=256):
     """The reference's PyTorch/Triton math restated for CPU (oracle port), timed on whole (batch, head)
     slices of the workload with all host threads; the bounded sample is scaled to the metric's unit."""
     from oracle import intfa_oracle as O
@@ -181,7 +181,7 @@ def run_reference_arm(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
