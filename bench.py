@@ -34,6 +34,8 @@ WORKLOADS = {
     "c3_half_b8_h32_n4096_d128_causal": ("half", 8, 32, 4096, 128, True, 1.0, True),
     "c4shard_full_b8_h64_n4096_d128": ("full", 8, 64, 4096, 128, False, 1.0, False),
     "c1_full_b1_h4_n512_d64": ("full", 1, 4, 512, 64, False, 1.0, False),
+    # long-context causal ring over all ranks (sequence-parallel; needs --gpus >= 2): N is the GLOBAL sequence
+    "c5_ring_full_b1_h32_n131072_d128_causal": ("full", 1, 32, 131072, 128, True, 0.5, False),
     # small cases of the same kernels for profiler captures (a few hundred MB on the device)
     "prof_full_b2_h16_n4096_d128": ("full", 2, 16, 4096, 128, False, 1.0, False),
     "prof_half_b2_h16_n4096_d128_causal": ("half", 2, 16, 4096, 128, True, 1.0, True),
@@ -178,6 +180,74 @@ def run_reference_arm(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_ring(args, pkg, dist, rank, world, local_rank, dev):
+    """Long-context causal full-int8 attention, sequence sharded zigzag over the ranks: every rank owns
+    half-chunks (rank, 2*world-1-rank) of the global sequence, quantises them (per-channel V absmax
+    all-reduced), and runs the ascending ring (int8 K/V + fp32 K scales by NCCL send/recv).  A step =
+    prologue + ring forward of the whole sequence; strong scaling (the global problem is fixed)."""
+    variant, B, H, N, D, causal, std, outlier = WORKLOADS[args.workload]
+    if world < 2:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "unavailable": "the ring workload needs --gpus >= 2"}), flush=True)
+        return
+    nh = N // (2 * world)
+    sm_scale = D ** -0.5
+    parts = []
+    for c in (rank, 2 * world - 1 - rank):            # each half-chunk from its own seed: independent of world size
+        g = torch.Generator(device=dev).manual_seed(5000 + c)
+        parts.append([std * torch.randn(B, H, nh, D, device=dev, generator=g, dtype=torch.float32) for _ in range(3)])
+    q, k, v = (torch.cat([parts[0][i], parts[1][i]], dim=2).half() for i in range(3))
+
+    def step():
+        q8, qs = pkg.quant_pertoken(q)
+        k8, ks = pkg.quant_pertoken(k)
+        v8, vs = pkg.shard.quantize_v_global(v, "per_channel")
+        return pkg.shard.ring_attention_causal(q8, k8, v8, qs, ks, vs, sm_scale, variant="full")
+
+    def barrier():
+        dist.barrier(device_ids=[local_rank])
+        torch.cuda.synchronize(dev)
+
+    steps = min(args.steps, 10)
+    for _ in range(args.warmup):
+        step()
+    pkg.check_status(dev)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    pkg.check_status(dev)
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    ops = attn_ops(B, H, N, D, True)
+    if rank == 0:
+        peaks, src = measured_peaks()
+        value = ops / (ms * 1e-3) / 1e12
+        kv_bytes = B * H * nh * (2 * D + 4)           # one int8 K + V half-chunk and its fp32 K scales
+        line = {"metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": world, "steps": steps, "warmup": args.warmup,
+                "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "s8",
+                "data": "synthetic",
+                "config": {"workload": args.workload, "variant": variant, "B": B, "H": H, "N_global": N, "D": D,
+                           "causal": True, "layout": "zigzag half-chunks, ascending ring, NCCL send/recv",
+                           "half_chunk_rows": nh, "bytes_per_half_chunk_transfer": kv_bytes,
+                           "l2": "inputs exceed L2"},
+                "clocks": clocks, "gpu_launches": steps * (5 + 2 * world + 1),
+                "roofline": {"bound": "tensor", "kernel": "intfa_fwd_kernel", "achieved": value / world,
+                             "peak": 2.0 * peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                             "frac": value / world / (2.0 * peaks["bf16_tflops_sustained"]), "traffic": None,
+                             "peak_source": "per GPU; 2 x MEASURED_PEAKS.bf16_tflops_sustained (%s)" % src},
+                "e2e": None, "cpu_baseline": None}
+        print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -209,6 +279,11 @@ def main():
     variant, B, H, N, D, causal, std, outlier = WORKLOADS[args.workload]
     full = variant == "full"
     sm_scale = D ** -0.5
+    if "ring" in args.workload:
+        run_ring(args, pkg, dist, rank, world, local_rank, dev)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     q, k, v = synth(B, H, N, D, std, outlier, 1000 + rank, dev)
 
     def step():
