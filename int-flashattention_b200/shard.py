@@ -11,8 +11,9 @@ from that structure:
   rows and their running (m, l, acc) state, and receives int8 K/V half-chunks plus fp32 K scales
   from their owners with point-to-point send/recv, in ASCENDING global order, so that every query
   row visits its keys in the same order and at the same running-max granularity as a
-  single-device pass (the full-int8 result depends on that order).  The transfer of half-chunk
-  c+1 is posted before the attention launch on half-chunk c, on a side stream.
+  single-device pass (the full-int8 result depends on that order).  Transfers are posted ahead of
+  the attention launches on a side stream (by default all of them at the start: the gathered int8
+  K/V of the whole sequence is ~1 GiB at 131072 tokens x 32 heads), landing in local HBM.
 
 The host logic here is backend-agnostic: it moves tensors with torch.distributed (NCCL on GPUs,
 gloo in CPU tests) and calls an `attend` function for the per-chunk forward, which defaults to
@@ -100,12 +101,14 @@ def _cuda_attend(variant, G):
 
 
 def ring_attention_causal(q8, k8, v, q_scale, k_scale, v_scale, sm_scale, *, variant="full", G=None,
-                          group=None, attend=None, comm_stream=None):
+                          group=None, attend=None, comm_stream=None, prefetch=None):
     """Causal attention over a sequence sharded zigzag across the ranks of `group`.
 
     Local inputs are [B,H,2*Nh,D] (q8,k8 int8; v int8 or fp16) with scales [B,H,2*Nh]; rows
     [0,Nh) are global half-chunk `rank`, rows [Nh,2Nh) are half-chunk 2P-1-rank.  v_scale must
-    already be the GLOBAL V scale (see quantize_v_global).  Returns the local o [B,H,2*Nh,D] fp16.
+    already be the GLOBAL V scale (see quantize_v_global).  `prefetch` = how many half-chunk
+    transfers are posted ahead of the attention launches (None = all of them at the start).
+    Returns the local o [B,H,2*Nh,D] fp16.
     """
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
@@ -119,11 +122,13 @@ def ring_attention_causal(q8, k8, v, q_scale, k_scale, v_scale, sm_scale, *, var
     q_half = [(q8[:, :, :nh], q_scale[:, :, :nh]), (q8[:, :, nh:], q_scale[:, :, nh:])]
     local_kv = {mine[0]: (k8[:, :, :nh].contiguous(), v[:, :, :nh].contiguous(), k_scale[:, :, :nh].contiguous().float()),
                 mine[1]: (k8[:, :, nh:].contiguous(), v[:, :, nh:].contiguous(), k_scale[:, :, nh:].contiguous().float())}
-    bufs = [tuple(torch.empty_like(t) for t in local_kv[mine[0]]) for _ in range(2)]
     state = [None, None]
     out = [None, None]
     if on_gpu and comm_stream is None:
         comm_stream = torch.cuda.Stream(device=q8.device)
+    n_chunks = 2 * world
+    depth = n_chunks if prefetch is None else max(1, int(prefetch))
+    free_bufs = []                      # receive buffers whose chunk has been consumed
 
     def post(c):
         """Start the transfer of KV half-chunk c (send if owned, recv if needed). Returns (tensors, works)."""
@@ -134,7 +139,7 @@ def ring_attention_causal(q8, k8, v, q_scale, k_scale, v_scale, sm_scale, *, var
                     for r in peers for t in local_kv[c]]
             tensors = local_kv[c]
         elif needs(rank, c, world):
-            tensors = bufs[c % 2]
+            tensors = free_bufs.pop() if free_bufs else tuple(torch.empty_like(t) for t in local_kv[mine[0]])
             src = dist.get_global_rank(group, own) if group is not None else own
             ops_ = [dist.P2POp(dist.irecv, t, src, group) for t in tensors]
         else:
@@ -142,34 +147,43 @@ def ring_attention_causal(q8, k8, v, q_scale, k_scale, v_scale, sm_scale, *, var
         if not ops_:
             return tensors, []
         if on_gpu:
-            comm_stream.wait_stream(torch.cuda.current_stream(q8.device))   # buffer reuse: after its last reader
+            comm_stream.wait_stream(torch.cuda.current_stream(q8.device))   # a reused buffer: after its last reader
             with torch.cuda.stream(comm_stream):
                 works = dist.batch_isend_irecv(ops_)
         else:
             works = dist.batch_isend_irecv(ops_)
         return tensors, works
 
-    n_chunks = 2 * world
-    pending = post(0)
+    # transfers are posted `depth` half-chunks ahead of the attention launches, in ascending order on
+    # every rank (so sends and receives of each pair match); by default all of them up front -- the
+    # gathered int8 K/V of the whole sequence is small next to HBM
+    pending = {}
+    nxt = 0
+    while nxt < min(depth, n_chunks):
+        pending[nxt] = post(nxt)
+        nxt += 1
     for c in range(n_chunks):
-        tensors, works = pending
-        pending = post(c + 1) if c + 1 < n_chunks else (None, [])
+        tensors, works = pending.pop(c)
         for w in works:
             w.wait()                      # GPU: makes the current stream wait for the transfer
-        if tensors is None:
-            continue
-        kc, vc, ksc = tensors
-        for h in range(2):
-            g = mine[h]                   # global half-chunk of this query half
-            if c > g:
-                continue
-            last = c == g
-            qh, qsh = q_half[h]
-            o, st = attend(qh, kc, vc, qsh, ksc, v_scale, sm_scale, g * nh, c * nh, state[h], last)
-            if last:
-                out[h] = o
-            else:
-                state[h] = st
+        if tensors is not None:
+            kc, vc, ksc = tensors
+            for h in range(2):
+                g = mine[h]               # global half-chunk of this query half
+                if c > g:
+                    continue
+                last = c == g
+                qh, qsh = q_half[h]
+                o, st = attend(qh, kc, vc, qsh, ksc, v_scale, sm_scale, g * nh, c * nh, state[h], last)
+                if last:
+                    out[h] = o
+                else:
+                    state[h] = st
+            if owner_of(c, world) != rank:
+                free_bufs.append(tensors)
+        if nxt < n_chunks:
+            pending[nxt] = post(nxt)
+            nxt += 1
     return torch.cat(out, dim=2)
 
 
