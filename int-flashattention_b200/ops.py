@@ -21,9 +21,13 @@ from . import _lib
 _status = {}          # device index -> int32[1] tensor the kernels report bounded-wait expiry into
 
 
-def default_G(head_dim):
-    """Running-max granularity used when the caller does not choose one: the widest KV tile
-    the reference's kernels allow for this head size (BLOCK_N <= HEAD_DIM, flash_atten_full_int8.py:88)."""
+def default_G(head_dim, variant="full"):
+    """Running-max granularity used when the caller does not choose one.  full-int8: the widest KV
+    tile the reference's kernels allow for this head size (BLOCK_N <= HEAD_DIM,
+    flash_atten_full_int8.py:88).  half-int8: 64 -- its result does not depend on G beyond fp16
+    rounding, and with 64-wide fp16 V/P tiles two CTAs fit on an SM."""
+    if variant == "half":
+        return 64
     return 128 if head_dim >= 128 else 64
 
 
@@ -101,7 +105,7 @@ def _fwd(variant, q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, *, G=Non
     B, H, Nq, D = q.shape
     Nk = k.shape[2]
     if G is None:
-        G = default_G(D)
+        G = default_G(D, variant)
     q, k, v = _prep_main(q), _prep_main(k), _prep_main(v)
     qs, ks = _scales_f32(q_scale), _scales_f32(k_scale)
     o = torch.empty((B, H, Nq, D) if write_o else (1, 1, 1, 8), dtype=torch.float16, device=q.device)  # :194-195

@@ -116,7 +116,7 @@ def ring_attention_causal(q8, k8, v, q_scale, k_scale, v_scale, sm_scale, *, var
     nh = N2 // 2
     if attend is None:
         from . import ops
-        attend = _cuda_attend(variant, G if G is not None else ops.default_G(D))
+        attend = _cuda_attend(variant, G if G is not None else ops.default_G(D, variant))
     on_gpu = q8.is_cuda
     mine = zigzag_chunks(world, rank)
     q_half = [(q8[:, :, :nh], q_scale[:, :, :nh]), (q8[:, :, nh:], q_scale[:, :, nh:])]
