@@ -34,6 +34,8 @@
 #include <stdint.h>
 #include <stdlib.h>
 
+#include <atomic>
+
 #include "intfa_internal.h"
 #include "intfa_ptx.cuh"
 
@@ -60,7 +62,7 @@ constexpr float kMagicF = 12582912.0f;
 // device-side wait codes stored in *status (low byte = which wait, bits 8.. = blockIdx)
 enum WaitCode {
   W_Q_EMPTY = 1, W_K_EMPTY, W_V_EMPTY, W_Q_FULL, W_K_FULL, W_V_FULL, W_P_FULL, W_O_EMPTY,
-  W_S_FULL, W_O_FULL, W_KS_FULL
+  W_S_FULL, W_O_FULL, W_KS_FULL, W_TILE
 };
 
 template <int D, int G, bool FULL>
@@ -84,9 +86,9 @@ struct Cfg {
   static constexpr int OFF_VSD = OFF_KS + NS * KS_BYTES;
   static constexpr int OFF_XCH = OFF_VSD + D * 4;             // half-row maxima / sums exchange: 2 x [2][128] float2 + [2][128] float
   static constexpr int OFF_BAR = OFF_XCH + 5 * 256 * 4;
-  static constexpr int NUM_BARS = 6 + 4 * NS;
+  static constexpr int NUM_BARS = 6 + 4 * NS + 8;              // + work-item ring: 4 x (published, consumed)
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
-  static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;   // +1024: manual alignment slack
+  static constexpr int SMEM_BYTES = OFF_MISC + 32 + 1024;   // misc: tmem slot, abort flag, 4 work-item slots; +1024: alignment slack
   // TMEM columns.  full: one int32 region shared by S = Q K^T (G columns) and O_j = P V (D columns) --
   // S is dead once P is written, O_j is dead once it is folded into the accumulator -- followed by the
   // fp32 accumulator (D columns).  half: S (G columns), then the fp32 accumulator the second MMA adds into.
@@ -166,8 +168,11 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   // B_OFULL: full = O_j ready (once per KV step); half = last PV of the work item done (once per work item).
   constexpr int B_QFULL = 0, B_QEMPTY = 1, B_SFULL = 2, B_PFULL = 3, B_OFULL = 4, B_RFREE = 5;
   constexpr int B_KFULL = 6, B_KEMPTY = 6 + NS, B_VFULL = 6 + 2 * NS, B_VEMPTY = 6 + 3 * NS;
+  constexpr int B_TILE = 6 + 4 * NS;       // work item published in ring slot i (see next_tile)
+  constexpr int B_TDONE = B_TILE + 4;      // ... and read by the MMA thread, the watcher and all 8 softmax warps
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 4);
+  volatile int* tile_slot = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 16);
 
   if (threadIdx.x == 0) {
     mbar_init(BAR(B_QFULL), 1);
@@ -181,6 +186,10 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(BAR(B_KEMPTY + s), 1);
       mbar_init(BAR(B_VFULL + s), 1);
       mbar_init(BAR(B_VEMPTY + s), 1);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(BAR(B_TILE + i), 1);
+      mbar_init(BAR(B_TDONE + i), 10);
     }
     *abort_flag = 0;
     mbar_init_fence();
@@ -198,6 +207,23 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tO = tmem_base + C::COL_O;
   const uint32_t tA = tmem_base + C::COL_ACC;
   const int code_hi = (int)(blockIdx.x << 8);
+
+  // Work items are handed out dynamically: the producer thread draws the next index from a global
+  // counter and publishes it in a 4-slot shared-memory ring; every other role reads the same
+  // sequence.  (The two CTAs sharing an SM do not run at the same speed, so a static split leaves
+  // one of them working alone at the end.)  The producer is never more than two items ahead of the
+  // slowest role.  Each reader (MMA thread, watcher, one lane per softmax warp: 10 arrivals) acknowledges
+  // a slot once it has read it; the producer waits for those before reusing the slot.  A negative index
+  // ends the sequence.
+  auto next_tile = [&](uint32_t& seq, bool ack, bool whole_warp) -> int {
+    const uint32_t slot = seq & 3u, par = (seq >> 2) & 1u;
+    ++seq;
+    if (!mbar_wait(BAR(B_TILE + slot), par, abort_flag, p.status, code_hi | W_TILE)) return -1;
+    const int t = tile_slot[slot];
+    if (whole_warp) __syncwarp();       // every lane has read the slot before lane 0 acknowledges it
+    if (ack) mbar_arrive(BAR(B_TDONE + slot));
+    return t;
+  };
 
   const uint32_t sQ = smem_u32(smem + C::OFF_Q);
   const uint32_t sK = smem_u32(smem + C::OFF_K);
@@ -225,7 +251,18 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       prefetch_tmap(&tmV);
       uint32_t kv_it = 0, tile_it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      uint32_t tseq = 0;
+      while (ok) {
+        if (tseq >= 4u) {       // slot reuse: everyone has read the item published four draws ago
+          ok = mbar_wait(BAR(B_TDONE + (tseq & 3u)), ((tseq >> 2) - 1u) & 1u, abort_flag, p.status, code_hi | W_TILE);
+          if (!ok) break;
+        }
+        int tile = (int)atomicAdd(p.tile_counter, 1u);
+        if (tile >= p.num_tiles) tile = -1;
+        tile_slot[tseq & 3u] = tile;
+        mbar_arrive(BAR(B_TILE + (tseq & 3u)));        // release: the slot is visible to the waiters
+        ++tseq;
+        if (tile < 0) break;
         const TileInfo t = decode_tile(p, tile, G);
         if (t.nsteps == 0) continue;
         ok = mbar_wait<kSleepProducer>(BAR(B_QEMPTY), (tile_it & 1) ^ 1, abort_flag, p.status, code_hi | W_Q_EMPTY);
@@ -272,7 +309,10 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         umma_commit(BAR(B_KEMPTY + s));
         return true;
       };
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      uint32_t tseq = 0;
+      while (ok) {
+        const int tile = next_tile(tseq, true, false);
+        if (tile < 0) break;
         const TileInfo t = decode_tile(p, tile, G);
         if (t.nsteps == 0) continue;
         ok = mbar_wait(BAR(B_QFULL), tile_it & 1, abort_flag, p.status, code_hi | W_Q_FULL);
@@ -340,7 +380,10 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // warps block in bar.sync (no issue slots) instead of polling; this one warp polls for them.
       uint32_t kv_it = 0, tile_it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      uint32_t tseq = 0;
+      while (ok) {
+        const int tile = next_tile(tseq, lane == 0, true);
+        if (tile < 0) break;
         const TileInfo t = decode_tile(p, tile, G);
         if (t.nsteps == 0) continue;
         for (int j = 0; ok && j < t.nsteps; ++j, ++kv_it) {
@@ -383,9 +426,18 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     bool ok = true;
 #ifdef INTFA_TIMING
     long long tm[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tq;
+    const long long life0 = clock64();
+    unsigned long long gt0;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt0));
 #endif
-    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+    uint32_t tseq = 0;
+    while (true) {
+      const int tile = next_tile(tseq, lane == 0, true);
+      if (tile < 0) break;
       const TileInfo t = decode_tile(p, tile, G);
+#ifdef INTFA_TIMING
+      const long long t_tile0 = clock64();
+#endif
       const long long rowg = (long long)t.bh * p.Nq + (long long)t.mb * kBM + row;   // row in [B*H*Nq)
       const long long grow = p.q_off + (long long)t.mb * kBM + row;                  // global position
       const float qs_r = p.qs[(long long)t.b * p.qs_sb + (long long)t.h * p.qs_sh + t.mb * kBM + row];
@@ -422,6 +474,10 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           vsd_s[ch] = p.vs[(long long)t.b * p.vs_sb + (long long)t.h * p.vs_sh + (long long)ch * p.vs_sd] / 127.0f;
         named_bar_sync(1, kComputeThreads);
       }
+#ifdef INTFA_TIMING
+      tm[6] += clock64() - t_tile0;
+      long long t_epi0 = 0;
+#endif
 
       for (int j = 0; ok && j < t.nsteps; ++j, ++step_it) {
         const uint32_t s = step_it % NS, ph = (step_it / NS) & 1;
@@ -450,14 +506,8 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll 1
         for (int cc = 0; cc < GH / 32; ++cc) {
           uint32_t r[32];
-#ifdef INTFA_TIMING
-          const long long tl0 = clock64();
-#endif
           tmem_ld32(tSh + cc * 32, r);
           tmem_ld_wait(r);
-#ifdef INTFA_TIMING
-          tm[6] += clock64() - tl0;
-#endif
           if (dbg_here) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) p.dbg_s[row * G + col0 + cc * 32 + i] = (int)(r[i] - kMagicI);
@@ -538,14 +588,8 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll 1
         for (int cc = 0; cc < GH / 32; ++cc) {
           uint32_t r[32];
-#ifdef INTFA_TIMING
-          const long long tl0 = clock64();
-#endif
           tmem_ld32(tSh + cc * 32, r);
           tmem_ld_wait(r);
-#ifdef INTFA_TIMING
-          tm[7] += clock64() - tl0;
-#endif
           tmem_fill32(tSh + cc * 32, kMagicI);
           uint32_t pk[FULL ? 8 : 16];
 #pragma unroll
@@ -674,6 +718,9 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
       if (!ok) break;
+#ifdef INTFA_TIMING
+      t_epi0 = clock64();
+#endif
 
       // ---- epilogue
       if constexpr (!FULL) {
@@ -734,9 +781,19 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           ++tile_it;
         }
       }
+#ifdef INTFA_TIMING
+      tm[7] += clock64() - t_epi0;
+#endif
     }
 #ifdef INTFA_TIMING
-    if (lane == 0 && p.dbg_s != nullptr && p.dbg_tile == -2 && blockIdx.x < 64 && half == 0) {
+    {
+      unsigned long long gt1;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt1));
+      tm[6] = clock64() - life0;          // CTA lifetime in SM cycles
+      tm[7] = (long long)(gt1 - gt0);     // and in nanoseconds
+      tm[5] = (long long)(gt0 & 0x3FFFFFFFull);   // start time stamp (ns, low bits)
+    }
+    if (lane == 0 && p.dbg_s != nullptr && p.dbg_tile == -2 && blockIdx.x < 400 && half == 0) {
       for (int i = 0; i < 8; ++i) p.dbg_s[(blockIdx.x * 4 + quarter) * 8 + i] = (int)(tm[i] >> 4);
     }
 #endif
@@ -770,6 +827,31 @@ static EncodeTiledFn get_encode_fn() {
       fn = reinterpret_cast<EncodeTiledFn>(ptr);
   }
   return fn;
+}
+
+// Work-item counters of the launches in flight: a small ring of words inside the library image (no
+// allocation at launch time); each launch takes the next word and zeroes it on its stream.
+constexpr int kTileCounters = 4096;
+__device__ static unsigned int g_tile_counters[kTileCounters];
+
+static int next_tile_counter(unsigned int** out, cudaStream_t stream) {
+  static unsigned int* base[64];
+  static bool have[64];
+  static std::atomic<unsigned int> next{0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return set_error(INTFA_ERR_CUDA, "cannot query the current device");
+  if (!have[dev]) {
+    void* sym = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&sym, g_tile_counters);
+    if (e != cudaSuccess || !sym) return set_error(INTFA_ERR_CUDA, "cudaGetSymbolAddress(tile counters): %s", cudaGetErrorString(e));
+    base[dev] = static_cast<unsigned int*>(sym);
+    have[dev] = true;
+  }
+  unsigned int* c = base[dev] + (next.fetch_add(1) % kTileCounters);
+  cudaError_t e = cudaMemsetAsync(c, 0, sizeof(unsigned int), stream);
+  if (e != cudaSuccess) return set_error(INTFA_ERR_CUDA, "cudaMemsetAsync(tile counter): %s", cudaGetErrorString(e));
+  *out = c;
+  return INTFA_OK;
 }
 
 // [B,H,N,D] tensor, element strides for (B,H,N); box = (box_d, box_rows, 1, 1)
@@ -821,7 +903,9 @@ static int launch(const IntfaFwdParams* a, const KParams& kp, cudaStream_t strea
   if (getenv("INTFA_ONE_CTA_PER_SM")) grid = sms;
 #endif
   if (grid > kp.num_tiles) grid = kp.num_tiles;
-  kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, kp);
+  KParams kpl = kp;
+  if ((rc = next_tile_counter(&kpl.tile_counter, stream))) return rc;
+  kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, kpl);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(INTFA_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(e));
   return INTFA_OK;

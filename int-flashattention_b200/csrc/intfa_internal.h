@@ -23,6 +23,7 @@ struct KParams {
   int* dbg_s; void* dbg_p; int dbg_tile, dbg_step;
   int* status;
   int MB, num_tiles;
+  unsigned int* tile_counter;    // zeroed word the CTAs draw work-item indices from
 };
 
 // Records the calling thread's last error (printf-style) and returns `code`.
