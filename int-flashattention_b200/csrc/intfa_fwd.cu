@@ -435,12 +435,14 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int tile = next_tile(tseq, lane == 0, true);
       if (tile < 0) break;
       const TileInfo t = decode_tile(p, tile, G);
-#ifdef INTFA_TIMING
-      const long long t_tile0 = clock64();
-#endif
       const long long rowg = (long long)t.bh * p.Nq + (long long)t.mb * kBM + row;   // row in [B*H*Nq)
       const long long grow = p.q_off + (long long)t.mb * kBM + row;                  // global position
       const float qs_r = p.qs[(long long)t.b * p.qs_sb + (long long)t.h * p.qs_sh + t.mb * kBM + row];
+      // (magic + S)*s_q - magic*s_q is S*s_q exactly, so when magic*s_q is representable (always for a
+      // scale that came from fp16) one fma yields the same rounded fp32(S)*s_q as subtract-then-multiply.
+      // Warps holding a row where it is not take the general path below.
+      const float mq = kMagicF * qs_r;
+      const bool fold = __all_sync(0xffffffffu, fmaf(kMagicF, qs_r, -mq) == 0.0f);
       float m_i = -INFINITY;
       float l_i = 1.0f;                                      // full row sum, kept identical in both threads of the row
       float ls_pend = 0.f, alpha_pend = 1.f;                 // this thread's half-row sum of the latest KV step, not yet
@@ -474,10 +476,6 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           vsd_s[ch] = p.vs[(long long)t.b * p.vs_sb + (long long)t.h * p.vs_sh + (long long)ch * p.vs_sd] / 127.0f;
         named_bar_sync(1, kComputeThreads);
       }
-#ifdef INTFA_TIMING
-      tm[6] += clock64() - t_tile0;
-      long long t_epi0 = 0;
-#endif
 
       for (int j = 0; ok && j < t.nsteps; ++j, ++step_it) {
         const uint32_t s = step_it % NS, ph = (step_it / NS) & 1;
@@ -513,14 +511,14 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (int i = 0; i < 32; ++i) p.dbg_s[row * G + col0 + cc * 32 + i] = (int)(r[i] - kMagicI);
           }
           const float4* k4 = reinterpret_cast<const float4*>(ks_s + cc * 32);
-          if (!masked) {
+          if (!masked && fold) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const float4 kk = k4[i];
-              const float s0 = ((__uint_as_float(r[4 * i + 0]) - kMagicF) * qs_r) * kk.x;
-              const float s1 = ((__uint_as_float(r[4 * i + 1]) - kMagicF) * qs_r) * kk.y;
-              const float s2 = ((__uint_as_float(r[4 * i + 2]) - kMagicF) * qs_r) * kk.z;
-              const float s3 = ((__uint_as_float(r[4 * i + 3]) - kMagicF) * qs_r) * kk.w;
+              const float s0 = fmaf(__uint_as_float(r[4 * i + 0]), qs_r, -mq) * kk.x;
+              const float s1 = fmaf(__uint_as_float(r[4 * i + 1]), qs_r, -mq) * kk.y;
+              const float s2 = fmaf(__uint_as_float(r[4 * i + 2]), qs_r, -mq) * kk.z;
+              const float s3 = fmaf(__uint_as_float(r[4 * i + 3]), qs_r, -mq) * kk.w;
               if (i & 1) {
                 mx2 = max3(mx2, s0, s1);
                 mx3 = max3(mx3, s2, s3);
@@ -538,7 +536,7 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const float sraw = ((__uint_as_float(r[i]) - kMagicF) * qs_r) * ks_s[cc * 32 + i];
-              const float x0 = fmaf(sraw, c, (gc0 + i <= grow) ? 0.f : -1.0e6f);
+              const float x0 = masked ? fmaf(sraw, c, (gc0 + i <= grow) ? 0.f : -1.0e6f) : sraw;
               mx0 = fmaxf(mx0, x0);
               r[i] = __float_as_uint(x0);
             }
@@ -718,9 +716,6 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
       if (!ok) break;
-#ifdef INTFA_TIMING
-      t_epi0 = clock64();
-#endif
 
       // ---- epilogue
       if constexpr (!FULL) {
@@ -781,18 +776,8 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           ++tile_it;
         }
       }
-#ifdef INTFA_TIMING
-      tm[7] += clock64() - t_epi0;
-#endif
     }
 #ifdef INTFA_TIMING
-    {
-      unsigned long long gt1;
-      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt1));
-      tm[6] = clock64() - life0;          // CTA lifetime in SM cycles
-      tm[7] = (long long)(gt1 - gt0);     // and in nanoseconds
-      tm[5] = (long long)(gt0 & 0x3FFFFFFFull);   // start time stamp (ns, low bits)
-    }
     if (lane == 0 && p.dbg_s != nullptr && p.dbg_tile == -2 && blockIdx.x < 400 && half == 0) {
       for (int i = 0; i < 8; ++i) p.dbg_s[(blockIdx.x * 4 + quarter) * 8 + i] = (int)(tm[i] >> 4);
     }

@@ -197,6 +197,22 @@ def test_bench_style_inputs_run(pkg, oracle, dev):
     _close(oracle, out.float() / scale, ref.float() / scale, tight=False)
 
 
+def test_arbitrary_fp32_scales(pkg, oracle, dev):
+    """Scales that are NOT fp16-representable take the kernel's general dequantisation path
+    (the one-fma shortcut is only exact for fp16-valued scales)."""
+    B, H, N, D = 1, 2, 384, 128
+    g = torch.Generator().manual_seed(9)
+    q8, k8, v8 = (torch.randint(-127, 128, (B, H, N, D), dtype=torch.int8, generator=g) for _ in range(3))
+    qs = torch.rand(B, H, N, generator=g) * 0.02 + 1e-3
+    ks = torch.rand(B, H, N, generator=g) * 0.02 + 1e-3
+    vs = torch.rand(B, H, D, generator=g) * 0.02 + 1e-3
+    for causal in (False, True):
+        ref = oracle.attention_full_int8(q8, k8, v8, qs, ks, vs, causal, 0.3, G=128)
+        out = pkg.attention_full_int8(q8.to(dev), k8.to(dev), v8.to(dev), qs.to(dev), ks.to(dev), vs.to(dev), causal, 0.3)
+        pkg.check_status()
+        _close(oracle, out, ref)
+
+
 def test_strided_qkv_layout(pkg, dev):
     """[B,N,H,D] storage viewed as [B,H,N,D] (the layout of the reference's CUDA path) needs no copy."""
     B, H, N, D = 2, 4, 256, 128
