@@ -63,7 +63,9 @@ typedef struct IntfaFwdParams {
   int32_t causal;               /* 0/1; mask is (kv_offset + col) <= (q_offset + row) */
   float   sm_scale;             /* natural-log softmax scale; kernel multiplies by 1.44269504 */
   int32_t G;                    /* running-max column granularity = KV tile width: 64 or 128
-                                   (the reference's BLOCK_N; full-int8 results depend on it) */
+                                   (the reference's BLOCK_N; full-int8 results depend on it).  The
+                                   reference only allows BLOCK_N <= HEAD_DIM (flash_atten_full_int8.py:88);
+                                   G=128 with D=64 is accepted here as a faster granularity of its own. */
   int32_t p_round;              /* 0: fp16(p)*127+0.5 truncated (Triton op); 1: fp32 p*127 RNE (CUDA path) */
   int64_t q_offset, kv_offset;  /* global position of row 0 / column 0 (ring attention); 0 otherwise */
   /* optional outputs / carried state, all fp32 and contiguous: m,l,lse [B,H,Nq]; acc [B,H,Nq,D] */

@@ -73,9 +73,6 @@ int intfa_fwd(const IntfaFwdParams* p, void* stream) {
   if (p->D != 64 && p->D != 128)
     return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: the sm_100a kernels cover 64 and 128", p->D);
   if (p->G != 64 && p->G != 128) return set_error(INTFA_ERR_UNSUPPORTED, "G=%d unsupported: 64 or 128", p->G);
-  if (p->G > p->D)
-    return set_error(INTFA_ERR_UNSUPPORTED, "G=%d > head_dim=%d unsupported (the reference requires BLOCK_N <= HEAD_DIM)",
-                     p->G, p->D);
   if (p->Nq % 128 != 0) return set_error(INTFA_ERR_UNSUPPORTED, "Nq=%d must be a multiple of 128", p->Nq);
   if (p->Nk % p->G != 0) return set_error(INTFA_ERR_UNSUPPORTED, "Nk=%d must be a multiple of G=%d", p->Nk, p->G);
   if (p->p_round != 0 && p->p_round != 1) return set_error(INTFA_ERR_INVALID_ARG, "p_round must be 0 or 1");

@@ -926,8 +926,9 @@ int fwd_dispatch(const IntfaFwdParams* a, cudaStream_t stream) {
   INTFA_CASE(128, 128)
   INTFA_CASE(128, 64)
   INTFA_CASE(64, 64)
+  INTFA_CASE(64, 128)
 #undef INTFA_CASE
-  return set_error(INTFA_ERR_UNSUPPORTED, "unsupported (D=%d, G=%d): supported are (128,128), (128,64), (64,64)", D, G);
+  return set_error(INTFA_ERR_UNSUPPORTED, "unsupported (D=%d, G=%d): supported are (128,128), (128,64), (64,64), (64,128)", D, G);
 }
 
 }  // namespace intfa

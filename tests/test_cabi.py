@@ -72,8 +72,8 @@ def test_validation_rejects_before_launch(lib):
     P.Nq = 100
     assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_UNSUPPORTED       # ragged Nq
     P.Nq = 128
-    P.D, P.G = 64, 128
-    assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_UNSUPPORTED       # G > head_dim
+    P.G = 96
+    assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_UNSUPPORTED       # G must be 64 or 128
     P.D, P.G = 128, 128
     assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_INVALID_ARG       # q is NULL
     P.variant = 7

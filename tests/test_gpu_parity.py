@@ -112,6 +112,8 @@ CASES = [
     (1, 2, 512, 128, 128, True),
     (1, 2, 512, 128, 64, True),
     (2, 2, 384, 64, 64, True),
+    (1, 2, 512, 64, 128, False),         # wider than the reference allows for d=64, same math
+    (1, 2, 512, 64, 128, True),
     (1, 1, 2048, 128, 128, True),
 ]
 
