@@ -12,7 +12,8 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB = os.path.join(PKG_DIR, "libintfa.so")
 SOURCES = ["intfa_api.cu", "intfa_quant.cu", "intfa_fwd.cu"]
-HEADERS = ["intfa_internal.h", "intfa_ptx.cuh", os.path.join("..", "..", "include", "intfa.h")]
+HEADERS = ["intfa_internal.h", "intfa_ptx.cuh", "intfa_fwd_pipe.cuh", "intfa_fwd_pipe_softmax.inc",
+           "intfa_fwd_pipe_update.inc", os.path.join("..", "..", "include", "intfa.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
 

@@ -35,6 +35,7 @@
 #include <stdlib.h>
 
 #include <atomic>
+#include <cstdlib>
 
 #include "intfa_internal.h"
 #include "intfa_ptx.cuh"
@@ -793,6 +794,8 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
+#include "intfa_fwd_pipe.cuh"
+
 // ============================================================================
 // host side
 // ============================================================================
@@ -896,6 +899,40 @@ static int launch(const IntfaFwdParams* a, const KParams& kp, cudaStream_t strea
   return INTFA_OK;
 }
 
+// Pipelined full-int8 kernel: one CTA per SM.
+template <int D, int G, bool PRNE>
+static int launch_pipe(const IntfaFwdParams* a, const KParams& kp, cudaStream_t stream) {
+  using C = PipeCfg<D, G>;
+  static_assert(C::SMEM_BYTES <= 227 * 1024, "shared memory");
+  CUtensorMap tmQ, tmK, tmV;
+  const CUtensorMapSwizzle swzD = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  int rc;
+  if ((rc = make_tmap(&tmQ, a->q, 1, a->q_stride, a->B, a->H, a->Nq, D, D, kBM, swzD))) return rc;
+  if ((rc = make_tmap(&tmK, a->k, 1, a->k_stride, a->B, a->H, a->Nk, D, D, G, swzD))) return rc;
+  if ((rc = make_tmap(&tmV, a->v, 1, a->v_stride, a->B, a->H, a->Nk, D, D, G, swzD))) return rc;
+  auto kern = intfa_fwd_pipe_kernel<D, G, PRNE>;
+  static bool attr_done = false;
+  static int attr_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_done || attr_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return set_error(INTFA_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    attr_done = true;
+    attr_dev = dev;
+  }
+  const int sms = sm_count_cached();
+  if (sms <= 0) return set_error(INTFA_ERR_CUDA, "cannot query SM count");
+  int grid = sms;
+  if (grid > kp.num_tiles) grid = kp.num_tiles;
+  KParams kpl = kp;
+  if ((rc = next_tile_counter(&kpl.tile_counter, stream))) return rc;
+  kern<<<grid, kPipeThreads, C::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, kpl);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(INTFA_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(e));
+  return INTFA_OK;
+}
+
 int fwd_dispatch(const IntfaFwdParams* a, cudaStream_t stream) {
   KParams kp;
   kp.qs = a->q_scale; kp.ks = a->k_scale; kp.vs = a->v_scale;
@@ -917,8 +954,11 @@ int fwd_dispatch(const IntfaFwdParams* a, cudaStream_t stream) {
   const bool full = a->variant == INTFA_VARIANT_FULL;
   const bool rne = full && a->p_round == 1;
   const int D = a->D, G = a->G;
+  static const bool use_pipe = getenv("INTFA_LEGACY_KERNEL") == nullptr;
 #define INTFA_CASE(DD, GG)                                                       \
   if (D == DD && G == GG) {                                                      \
+    if (full && use_pipe) return rne ? launch_pipe<DD, GG, true>(a, kp, stream)  \
+                                     : launch_pipe<DD, GG, false>(a, kp, stream);\
     if (full) return rne ? launch<DD, GG, true, true>(a, kp, stream)             \
                          : launch<DD, GG, true, false>(a, kp, stream);           \
     return launch<DD, GG, false, false>(a, kp, stream);                          \

@@ -1,0 +1,315 @@
+// Full-int8 attention forward, pipelined variant: ONE CTA per SM, one 128-row query tile at a time,
+// with the softmax of KV step j+1 overlapping the second MMA and the accumulator update of step j.
+// (Included by intfa_fwd.cu inside namespace intfa, after the shared helpers.)
+//
+// 512 threads:
+//   warp 0        TMA producer (Q once per work item; K, V and the K-scale slice through an NS-stage ring)
+//   warp 1        MMA issuer (one thread)
+//   warp 2        TMEM allocator; warp 3 idle
+//   warps 4-11    softmax, two threads per query row: S (TMEM) -> registers, dequantise, row max,
+//                 p = exp2, P -> shared memory (double buffered).  S is in registers after the
+//                 first pass, so the next Q K^T is issued while these warps are still in exp2.
+//   warps 12-15   accumulator update and epilogue, one thread per query row:
+//                 acc = acc*alpha + fp32(O_j)*s_v/127 with acc (fp32) and O_j (int32) both in TMEM;
+//                 alpha and the final (m, l) come from the softmax warps through shared memory.
+// TMEM columns: S [0,G) | O_j [G, G+D) | acc [G+D, G+2D)  (<= 384 of the 512 allocated).
+// S and O_j are int32 accumulators that start each KV step from the bit pattern of 1.5*2^23, written by a
+// small fp16 MMA ahead of the int8 MMAs, so that the threads read fp32(S32) + 1.5*2^23 without a conversion.
+// Arithmetic is the same as in intfa_fwd_kernel (see the contract at the top of intfa_fwd.cu).
+#pragma once
+
+constexpr int kPipeThreads = 512;
+constexpr int kPipeSoftmaxThreads = 256;
+constexpr int kPipeCorrThreads = 128;
+constexpr int kPipeServiceRegs = 40, kPipeSoftmaxRegs = 168, kPipeCorrRegs = 104;   // 128*40 + 256*168 + 128*104 <= 65536
+
+template <int D, int G>
+struct PipeCfg {
+  static constexpr int Q_BYTES = kBM * D;
+  static constexpr int K_BYTES = G * D;
+  static constexpr int V_BYTES = G * D;
+  static constexpr int P_BYTES = kBM * G;
+  static constexpr int KS_BYTES = G * 4;
+  static constexpr int NS = 4;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + Q_BYTES;
+  static constexpr int OFF_V = OFF_K + NS * K_BYTES;
+  static constexpr int OFF_P = OFF_V + NS * V_BYTES;              // two P buffers
+  static constexpr int OFF_KS = OFF_P + 2 * P_BYTES;
+  static constexpr int OFF_VSD = OFF_KS + NS * KS_BYTES;          // s_v/127 per channel
+  static constexpr int OFF_XCH = OFF_VSD + D * 4;                 // [2][2][128] float2: half-row max / sum exchange
+  static constexpr int OFF_ALPHA = OFF_XCH + 2 * 256 * 8;         // [4][128] float: alpha of step j for the updater
+  static constexpr int OFF_FIN = OFF_ALPHA + 4 * 128 * 4;         // [2][128] float2: final (m, l) of a work item
+  static constexpr int OFF_MAGIC = OFF_FIN + 2 * 128 * 8;          // 4 KB constant fp16 operand of the "arm" MMA
+  static constexpr int MAGIC_BYTES = 4096;
+  static constexpr int OFF_BAR = OFF_MAGIC + MAGIC_BYTES;
+  static constexpr int NUM_BARS = 12 + 4 * NS + 8;
+  static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
+  static constexpr int SMEM_BYTES = OFF_MISC + 32 + 1024;
+  static constexpr int COL_S = 0, COL_O = G, COL_ACC = G + D;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr uint64_t SWZ_QK = (D == 128) ? kSwz128 : kSwz64;
+  static constexpr uint32_t SBO_QK = 8 * D;
+  static constexpr uint64_t SWZ_P = (G == 128) ? kSwz128 : kSwz64;
+  static constexpr uint32_t SBO_P = 8 * G;
+  static constexpr uint64_t SWZ_V = (D == 128) ? kSwz128 : kSwz64;
+  static constexpr uint32_t SBO_V = 8 * D;
+  static constexpr uint32_t IDESC_QK = make_idesc(2, 1, 1, 0, 0, kBM, G);
+  static constexpr uint32_t IDESC_PV = make_idesc(2, 1, 1, 0, 1, kBM, D);
+  // fp16 x fp16 -> fp32, K = 16: writes the fp32 constant 1.5*2^23 into a whole accumulator tile
+  static constexpr uint32_t IDESC_ARM_S = make_idesc(1, 0, 0, 0, 0, kBM, G);
+  static constexpr uint32_t IDESC_ARM_O = make_idesc(1, 0, 0, 0, 0, kBM, D);
+};
+
+enum PipeWait { PW_TILE = 32, PW_QE, PW_KE, PW_VE, PW_QF, PW_KF, PW_VF, PW_SFREE, PW_PFULL, PW_OFREE, PW_SFULL,
+                PW_PFREE, PW_OFULL, PW_FIN, PW_FINFREE };
+
+template <int D, int G, bool PRNE>
+__global__ void __launch_bounds__(kPipeThreads, 1)
+intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, const KParams p) {
+  using C = PipeCfg<D, G>;
+  constexpr int NS = C::NS;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const uint32_t bar0 = smem_u32(smem + C::OFF_BAR);
+  auto BAR = [&](int i) { return bar0 + 8u * i; };
+  // mbarriers.  "commit" = arrived on by tcgen05.commit, i.e. when the MMAs issued so far are done.
+  constexpr int B_QFULL = 0;      // TMA: Q tile landed
+  constexpr int B_QEMPTY = 1;     // commit: last Q K^T of the work item done
+  constexpr int B_SFULL = 2;      // commit: S = Q K^T in TMEM
+  constexpr int B_SFREE = 3;      // softmax (8 warps): S copied to registers and re-armed
+  constexpr int B_PFULL = 4;      // softmax (8 warps): P of this step in shared memory
+  constexpr int B_PFREE = 5;      // [2] commit: the P V that read P buffer b is done
+  constexpr int B_OFULL = 7;      // commit: O_j = P V in TMEM
+  constexpr int B_OFREE = 8;      // updater (4 warps): O_j folded in and re-armed
+  constexpr int B_FIN = 9;        // softmax (4 half-0 warps): final (m, l) of the work item published
+  constexpr int B_FINFREE = 10;   // [2] updater (4 warps): it has read them
+  constexpr int B_KFULL = 12, B_KEMPTY = 12 + NS, B_VFULL = 12 + 2 * NS, B_VEMPTY = 12 + 3 * NS;
+  constexpr int B_TILE = 12 + 4 * NS, B_TDONE = B_TILE + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 4);
+  volatile int* tile_slot = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 16);
+
+  if (threadIdx.x == 0) {
+    mbar_init(BAR(B_QFULL), 1);
+    mbar_init(BAR(B_QEMPTY), 1);
+    mbar_init(BAR(B_SFULL), 1);
+    mbar_init(BAR(B_SFREE), 8);
+    mbar_init(BAR(B_PFULL), 8);
+    mbar_init(BAR(B_PFREE), 1);
+    mbar_init(BAR(B_PFREE + 1), 1);
+    mbar_init(BAR(B_OFULL), 1);
+    mbar_init(BAR(B_OFREE), 4);
+    mbar_init(BAR(B_FIN), 4);
+    mbar_init(BAR(B_FINFREE), 4);
+    mbar_init(BAR(B_FINFREE + 1), 4);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(BAR(B_KFULL + s), 1);
+      mbar_init(BAR(B_KEMPTY + s), 1);
+      mbar_init(BAR(B_VFULL + s), 1);
+      mbar_init(BAR(B_VEMPTY + s), 1);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(BAR(B_TILE + i), 1);
+      mbar_init(BAR(B_TDONE + i), 13);       // MMA thread + 8 softmax warps + 4 updater warps
+    }
+    *abort_flag = 0;
+    mbar_init_fence();
+    fence_proxy_async_smem();
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base + C::COL_S;
+  const uint32_t tO = tmem_base + C::COL_O;
+  const uint32_t tA = tmem_base + C::COL_ACC;
+  const int code_hi = (int)(blockIdx.x << 8);
+  const uint32_t sQ = smem_u32(smem + C::OFF_Q);
+  const uint32_t sK = smem_u32(smem + C::OFF_K);
+  const uint32_t sV = smem_u32(smem + C::OFF_V);
+  const uint32_t sP = smem_u32(smem + C::OFF_P);
+  const uint32_t sKS = smem_u32(smem + C::OFF_KS);
+
+  // The int32 accumulator tiles start every KV step from the bit pattern of 1.5*2^23 (see kMagicI).  It is
+  // written by the tensor core itself: an fp16 MMA (K = 16, no accumulate) of a constant operand with
+  // itself.  Every 16-byte chunk of the operand holds (1024, 1024, 2048, 0, 0, 0, 0, 0), so whatever the
+  // layout each row's 16 values are two such chunks and the dot product of any two rows is
+  // 2*(2^20 + 2^20 + 2^22) = 12582912 = 1.5*2^23, exactly, in fp32.
+  if (threadIdx.x < C::MAGIC_BYTES / 16) {
+    reinterpret_cast<uint4*>(smem + C::OFF_MAGIC)[threadIdx.x] = make_uint4(0x64006400u, 0x00006800u, 0u, 0u);
+    fence_proxy_async_smem();
+  }
+  __syncthreads();
+  const uint64_t descArm = make_smem_desc(smem_u32(smem + C::OFF_MAGIC), 128, 256, 0);
+
+  // work items: drawn from a global counter by the producer, published in a 4-slot ring (as in intfa_fwd_kernel)
+  auto next_tile = [&](uint32_t& seq, bool ack, bool whole_warp) -> int {
+    const uint32_t slot = seq & 3u, par = (seq >> 2) & 1u;
+    ++seq;
+    bool got = mbar_wait(BAR(B_TILE + slot), par, abort_flag, p.status, code_hi | PW_TILE);
+    if (whole_warp) got = __all_sync(0xffffffffu, got);
+    if (!got) return -1;
+    const int t = tile_slot[slot];
+    if (whole_warp) __syncwarp();
+    if (ack) mbar_arrive(BAR(B_TDONE + slot));
+    return t;
+  };
+
+  // registers: 512 x 128 at launch; the service warps and the accumulator warps give theirs to the softmax warps
+  if (warp < 4) reg_dealloc<kPipeServiceRegs>();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      prefetch_tmap(&tmQ);
+      prefetch_tmap(&tmK);
+      prefetch_tmap(&tmV);
+      uint32_t kv_it = 0, tile_it = 0, tseq = 0;
+      bool ok = true;
+      while (ok) {
+        if (tseq >= 4u) {
+          ok = mbar_wait(BAR(B_TDONE + (tseq & 3u)), ((tseq >> 2) - 1u) & 1u, abort_flag, p.status, code_hi | PW_TILE);
+          if (!ok) break;
+        }
+        int tile = (int)atomicAdd(p.tile_counter, 1u);
+        if (tile >= p.num_tiles) tile = -1;
+        tile_slot[tseq & 3u] = tile;
+        mbar_arrive(BAR(B_TILE + (tseq & 3u)));
+        ++tseq;
+        if (tile < 0) break;
+        const TileInfo t = decode_tile(p, tile, G);
+        if (t.nsteps == 0) continue;
+        ok = mbar_wait(BAR(B_QEMPTY), (tile_it & 1) ^ 1, abort_flag, p.status, code_hi | PW_QE);
+        if (!ok) break;
+        mbar_expect_tx(BAR(B_QFULL), C::Q_BYTES);
+        tma_load_4d(sQ, &tmQ, BAR(B_QFULL), 0, t.mb * kBM, t.h, t.b);
+        const float* ks_row = p.ks + (long long)t.b * p.ks_sb + (long long)t.h * p.ks_sh;
+        for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
+          const uint32_t s = kv_it % NS, ph = (kv_it / NS) & 1;
+          ok = mbar_wait(BAR(B_KEMPTY + s), ph ^ 1, abort_flag, p.status, code_hi | PW_KE);
+          if (!ok) break;
+          mbar_expect_tx(BAR(B_KFULL + s), C::K_BYTES + C::KS_BYTES);
+          tma_load_4d(sK + s * C::K_BYTES, &tmK, BAR(B_KFULL + s), 0, j * G, t.h, t.b);
+          bulk_load_1d(sKS + s * C::KS_BYTES, ks_row + j * G, C::KS_BYTES, BAR(B_KFULL + s));
+          ok = mbar_wait(BAR(B_VEMPTY + s), ph ^ 1, abort_flag, p.status, code_hi | PW_VE);
+          if (!ok) break;
+          mbar_expect_tx(BAR(B_VFULL + s), C::V_BYTES);
+          tma_load_4d(sV + s * C::V_BYTES, &tmV, BAR(B_VFULL + s), 0, j * G, t.h, t.b);
+        }
+        ++tile_it;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    {
+      // ------------------------------------------------------------------ MMA issuer
+      // The whole warp runs the loop and the waits (warp-uniform control flow keeps the descriptor arithmetic
+      // off the per-thread path); one elected lane issues the tensor-core instructions.
+      // order per work item: QK(0); then for each step j: [S free] QK(j+1), [P(j) ready, O free] PV(j).
+      uint32_t kv_it = 0, tile_it = 0, tseq = 0;
+      bool ok = true;
+#ifdef INTFA_TIMING
+      long long tm[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tq;
+#endif
+      // operand descriptors of stage 0 / K step 0; the start-address field (16-byte units) takes the offsets
+      const uint64_t descQ0 = make_smem_desc(sQ, 16, C::SBO_QK, C::SWZ_QK);
+      const uint64_t descK0 = make_smem_desc(sK, 16, C::SBO_QK, C::SWZ_QK);
+      const uint64_t descP0 = make_smem_desc(sP, 16, C::SBO_P, C::SWZ_P);
+      const uint64_t descV0 = make_smem_desc(sV, 16, C::SBO_V, C::SWZ_V);
+      auto issue_qk = [&](uint32_t it, bool last) -> bool {
+        const uint32_t s = it % NS, ph = (it / NS) & 1;
+        // S must have been copied out and re-armed by the softmax warps (step it-1)
+        INTFA_T0();
+        if (!mbar_wait_warp(BAR(B_SFREE), (it & 1) ^ 1, abort_flag, p.status, code_hi | PW_SFREE)) return false;
+        INTFA_T(0);
+        if (!mbar_wait_warp(BAR(B_KFULL + s), ph, abort_flag, p.status, code_hi | PW_KF)) return false;
+        tc_fence_after();
+        INTFA_T(1);
+        const uint64_t bd0 = descK0 + (uint64_t)(s * (C::K_BYTES >> 4));
+        if (elect_one()) {
+          umma_f16(tS, descArm, descArm, C::IDESC_ARM_S, 0);
+#pragma unroll
+          for (int kk = 0; kk < D / 32; ++kk) umma_i8(tS, descQ0 + 2 * kk, bd0 + 2 * kk, C::IDESC_QK, 1);
+          umma_commit(BAR(B_SFULL));
+          if (last) umma_commit(BAR(B_QEMPTY));
+        }
+        __syncwarp();
+        INTFA_T(2);
+        return true;
+      };
+      while (ok) {
+        const int tile = next_tile(tseq, lane == 0, true);
+        if (tile < 0) break;
+        const TileInfo t = decode_tile(p, tile, G);
+        if (t.nsteps == 0) continue;
+        ok = mbar_wait_warp(BAR(B_QFULL), tile_it & 1, abort_flag, p.status, code_hi | PW_QF);
+        if (!ok) break;
+        ok = issue_qk(kv_it, t.nsteps == 1);
+        if (!ok) break;
+        for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
+          const uint32_t s = kv_it % NS, ph = (kv_it / NS) & 1;
+          if (j + 1 < t.nsteps) {
+            ok = issue_qk(kv_it + 1, j + 2 == t.nsteps);
+            if (!ok) break;
+          }
+          INTFA_T0();
+          ok = mbar_wait_warp(BAR(B_PFULL), kv_it & 1, abort_flag, p.status, code_hi | PW_PFULL);
+          if (!ok) break;
+          INTFA_T(3);
+          // K stage of this step: the K scales in it have been read by the softmax warps (they arrived P)
+          if (elect_one()) umma_commit(BAR(B_KEMPTY + s));
+          __syncwarp();
+          ok = mbar_wait_warp(BAR(B_VFULL + s), ph, abort_flag, p.status, code_hi | PW_VF);
+          if (!ok) break;
+          INTFA_T(4);
+          ok = mbar_wait_warp(BAR(B_OFREE), (kv_it & 1) ^ 1, abort_flag, p.status, code_hi | PW_OFREE);
+          if (!ok) break;
+          tc_fence_after();
+          INTFA_T(5);
+          const uint64_t ad0 = descP0 + (uint64_t)((kv_it & 1) * (C::P_BYTES >> 4));
+          const uint64_t vd0 = descV0 + (uint64_t)(s * (C::V_BYTES >> 4));
+          if (elect_one()) {
+            umma_f16(tO, descArm, descArm, C::IDESC_ARM_O, 0);
+#pragma unroll
+            for (int kk = 0; kk < G / 32; ++kk) umma_i8(tO, ad0 + 2 * kk, vd0 + kk * ((32 * D) >> 4), C::IDESC_PV, 1);
+            umma_commit(BAR(B_OFULL));
+            umma_commit(BAR(B_VEMPTY + s));
+            umma_commit(BAR(B_PFREE + (kv_it & 1)));
+          }
+          __syncwarp();
+          INTFA_T(6);
+        }
+        ++tile_it;
+      }
+#ifdef INTFA_TIMING
+      if (lane == 0 && p.dbg_s != nullptr && p.dbg_tile == -2 && blockIdx.x < 400) {
+        for (int i = 0; i < 8; ++i) p.dbg_s[12800 + blockIdx.x * 8 + i] = (int)(tm[i] >> 4);
+      }
+#endif
+    }
+    __syncwarp();
+  } else if (warp >= 4 && warp < 12) {
+    reg_alloc<kPipeSoftmaxRegs>();
+#include "intfa_fwd_pipe_softmax.inc"
+  } else if (warp >= 12) {
+    reg_dealloc<kPipeCorrRegs>();
+#include "intfa_fwd_pipe_update.inc"
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
