@@ -1,27 +1,33 @@
-// Full-int8 attention forward, pipelined variant: ONE CTA per SM, one 128-row query tile at a time,
-// with the softmax of KV step j+1 overlapping the second MMA and the accumulator update of step j.
+// Full-int8 attention forward, pipelined variant: ONE CTA per SM, one 128-row query tile at a time.
 // (Included by intfa_fwd.cu inside namespace intfa, after the shared helpers.)
 //
-// 512 threads:
+// 640 threads:
 //   warp 0        TMA producer (Q once per work item; K, V and the K-scale slice through an NS-stage ring)
-//   warp 1        MMA issuer (one thread)
+//   warp 1        MMA issuer (whole warp runs the loop, one elected lane issues)
 //   warp 2        TMEM allocator; warp 3 idle
-//   warps 4-11    softmax, two threads per query row: S (TMEM) -> registers, dequantise, row max,
-//                 p = exp2, P -> shared memory (double buffered).  S is in registers after the
-//                 first pass, so the next Q K^T is issued while these warps are still in exp2.
-//   warps 12-15   accumulator update and epilogue, one thread per query row:
-//                 acc = acc*alpha + fp32(O_j)*s_v/127 with acc (fp32) and O_j (int32) both in TMEM;
-//                 alpha and the final (m, l) come from the softmax warps through shared memory.
-// TMEM columns: S [0,G) | O_j [G, G+D) | acc [G+D, G+2D)  (<= 384 of the 512 allocated).
+//   warps 4-7     softmax group 0, warps 8-11 softmax group 1: one thread per query row.  The groups take
+//                 ALTERNATE KV steps (group g owns the steps whose running index is g mod 2), each with its own
+//                 S buffer in TMEM and its own P buffer in shared memory, so that on every scheduler one
+//                 warp is in pass A (dequantise, row max: FMA pipe) while the other is in pass B (exp2, P:
+//                 MUFU).  The running max m and row sum l of a row travel between the two threads that own
+//                 it through shared memory, once per step each.
+//   warps 12-19   accumulator update and epilogue, two threads per query row (half the channels each):
+//                 acc = acc*alpha + fp32(O_j)*s_v/127 with acc (fp32) and O_j (int32) both in TMEM.
+// TMEM columns: S0 [0,G) | S1 [G,2G) | O_j [2G, 2G+D) | acc [2G+D, 2G+2D)  (<= 512).
 // S and O_j are int32 accumulators that start each KV step from the bit pattern of 1.5*2^23, written by a
 // small fp16 MMA ahead of the int8 MMAs, so that the threads read fp32(S32) + 1.5*2^23 without a conversion.
 // Arithmetic is the same as in intfa_fwd_kernel (see the contract at the top of intfa_fwd.cu).
 #pragma once
 
-constexpr int kPipeThreads = 512;
+constexpr int kPipeThreads = 640;
 constexpr int kPipeSoftmaxThreads = 256;
-constexpr int kPipeCorrThreads = 128;
-constexpr int kPipeServiceRegs = 40, kPipeSoftmaxRegs = 168, kPipeCorrRegs = 104;   // 128*40 + 256*168 + 128*104 <= 65536
+constexpr int kPipeCorrThreads = 256;
+// Registers: the CTA is launched with kPipeLaunchRegs per thread and setmaxnreg only moves registers around
+// INSIDE that allocation -- an increase beyond it would block for ever, hence the static_assert.
+constexpr int kPipeLaunchRegs = (65536 / kPipeThreads) / 8 * 8;
+constexpr int kPipeServiceRegs = 40, kPipeSoftmaxRegs = 128, kPipeCorrRegs = 80;
+static_assert(128 * kPipeServiceRegs + kPipeSoftmaxThreads * kPipeSoftmaxRegs + kPipeCorrThreads * kPipeCorrRegs <=
+                  kPipeThreads * kPipeLaunchRegs, "setmaxnreg budget exceeds the registers the CTA is launched with");
 
 template <int D, int G>
 struct PipeCfg {
@@ -37,16 +43,17 @@ struct PipeCfg {
   static constexpr int OFF_P = OFF_V + NS * V_BYTES;              // two P buffers
   static constexpr int OFF_KS = OFF_P + 2 * P_BYTES;
   static constexpr int OFF_VSD = OFF_KS + NS * KS_BYTES;          // s_v/127 per channel
-  static constexpr int OFF_XCH = OFF_VSD + D * 4;                 // [2][2][128] float2: half-row max / sum exchange
-  static constexpr int OFF_ALPHA = OFF_XCH + 2 * 256 * 8;         // [4][128] float: alpha of step j for the updater
+  static constexpr int OFF_HM = OFF_VSD + D * 4;                  // [2 groups][128] float: running max after the group's latest step
+  static constexpr int OFF_HL = OFF_HM + 2 * 128 * 4;             // [2 groups][128] float: row sum after the group's latest step
+  static constexpr int OFF_ALPHA = OFF_HL + 2 * 128 * 4;          // [4][128] float: alpha of step j for the updater
   static constexpr int OFF_FIN = OFF_ALPHA + 4 * 128 * 4;         // [2][128] float2: final (m, l) of a work item
   static constexpr int OFF_MAGIC = OFF_FIN + 2 * 128 * 8;          // 4 KB constant fp16 operand of the "arm" MMA
   static constexpr int MAGIC_BYTES = 4096;
   static constexpr int OFF_BAR = OFF_MAGIC + MAGIC_BYTES;
-  static constexpr int NUM_BARS = 12 + 4 * NS + 8;
+  static constexpr int NUM_BARS = 17 + 4 * NS + 8;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 32 + 1024;
-  static constexpr int COL_S = 0, COL_O = G, COL_ACC = G + D;
+  static constexpr int COL_S = 0, COL_O = 2 * G, COL_ACC = 2 * G + D;   // S buffer b at COL_S + b*G
   static constexpr int TMEM_COLS = 512;
   static constexpr uint64_t SWZ_QK = (D == 128) ? kSwz128 : kSwz64;
   static constexpr uint32_t SBO_QK = 8 * D;
@@ -62,7 +69,7 @@ struct PipeCfg {
 };
 
 enum PipeWait { PW_TILE = 32, PW_QE, PW_KE, PW_VE, PW_QF, PW_KF, PW_VF, PW_SFREE, PW_PFULL, PW_OFREE, PW_SFULL,
-                PW_PFREE, PW_OFULL, PW_FIN, PW_FINFREE };
+                PW_PFREE, PW_OFULL, PW_FIN, PW_FINFREE, PW_HM, PW_HL };
 
 template <int D, int G, bool PRNE>
 __global__ void __launch_bounds__(kPipeThreads, 1)
@@ -80,16 +87,17 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   // mbarriers.  "commit" = arrived on by tcgen05.commit, i.e. when the MMAs issued so far are done.
   constexpr int B_QFULL = 0;      // TMA: Q tile landed
   constexpr int B_QEMPTY = 1;     // commit: last Q K^T of the work item done
-  constexpr int B_SFULL = 2;      // commit: S = Q K^T in TMEM
-  constexpr int B_SFREE = 3;      // softmax (8 warps): S copied to registers and re-armed
-  constexpr int B_PFULL = 4;      // softmax (8 warps): P of this step in shared memory
-  constexpr int B_PFREE = 5;      // [2] commit: the P V that read P buffer b is done
-  constexpr int B_OFULL = 7;      // commit: O_j = P V in TMEM
-  constexpr int B_OFREE = 8;      // updater (4 warps): O_j folded in and re-armed
-  constexpr int B_FIN = 9;        // softmax (4 half-0 warps): final (m, l) of the work item published
-  constexpr int B_FINFREE = 10;   // [2] updater (4 warps): it has read them
-  constexpr int B_KFULL = 12, B_KEMPTY = 12 + NS, B_VFULL = 12 + 2 * NS, B_VEMPTY = 12 + 3 * NS;
-  constexpr int B_TILE = 12 + 4 * NS, B_TDONE = B_TILE + 4;
+  constexpr int B_SFULL = 2;      // [2] commit: S = Q K^T in TMEM buffer b
+  constexpr int B_PFULL = 4;      // [2] softmax group b (4 warps): P in shared-memory buffer b, and S buffer b read out
+  constexpr int B_PFREE = 6;      // [2] commit: the P V that read P buffer b is done
+  constexpr int B_OFULL = 8;      // commit: O_j = P V in TMEM
+  constexpr int B_OFREE = 9;      // updater (8 warps): O_j read out
+  constexpr int B_FIN = 10;       // softmax (4 warps of one group): final (m, l) of the work item published
+  constexpr int B_FINFREE = 11;   // [2] updater (8 warps): it has read them
+  constexpr int B_HM = 13;        // [2] softmax group g (4 warps): running max after its step published
+  constexpr int B_HL = 15;        // [2] softmax group g (4 warps): row sum after its step published
+  constexpr int B_KFULL = 17, B_KEMPTY = 17 + NS, B_VFULL = 17 + 2 * NS, B_VEMPTY = 17 + 3 * NS;
+  constexpr int B_TILE = 17 + 4 * NS, B_TDONE = B_TILE + 4;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 4);
   volatile int* tile_slot = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 16);
@@ -97,16 +105,17 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   if (threadIdx.x == 0) {
     mbar_init(BAR(B_QFULL), 1);
     mbar_init(BAR(B_QEMPTY), 1);
-    mbar_init(BAR(B_SFULL), 1);
-    mbar_init(BAR(B_SFREE), 8);
-    mbar_init(BAR(B_PFULL), 8);
-    mbar_init(BAR(B_PFREE), 1);
-    mbar_init(BAR(B_PFREE + 1), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(BAR(B_SFULL + b), 1);
+      mbar_init(BAR(B_PFULL + b), 4);
+      mbar_init(BAR(B_PFREE + b), 1);
+      mbar_init(BAR(B_FINFREE + b), 8);
+      mbar_init(BAR(B_HM + b), 4);
+      mbar_init(BAR(B_HL + b), 4);
+    }
     mbar_init(BAR(B_OFULL), 1);
-    mbar_init(BAR(B_OFREE), 4);
+    mbar_init(BAR(B_OFREE), 8);
     mbar_init(BAR(B_FIN), 4);
-    mbar_init(BAR(B_FINFREE), 4);
-    mbar_init(BAR(B_FINFREE + 1), 4);
     for (int s = 0; s < NS; ++s) {
       mbar_init(BAR(B_KFULL + s), 1);
       mbar_init(BAR(B_KEMPTY + s), 1);
@@ -115,7 +124,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(BAR(B_TILE + i), 1);
-      mbar_init(BAR(B_TDONE + i), 13);       // MMA thread + 8 softmax warps + 4 updater warps
+      mbar_init(BAR(B_TDONE + i), 17);       // MMA warp + 8 softmax warps + 8 updater warps
     }
     *abort_flag = 0;
     mbar_init_fence();
@@ -214,7 +223,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       // ------------------------------------------------------------------ MMA issuer
       // The whole warp runs the loop and the waits (warp-uniform control flow keeps the descriptor arithmetic
       // off the per-thread path); one elected lane issues the tensor-core instructions.
-      // order per work item: QK(0); then for each step j: [S free] QK(j+1), [P(j) ready, O free] PV(j).
+      // Order per work item: QK(0), QK(1); then for each step j: [P(j) ready = S buffer of j free] QK(j+2), PV(j).
       uint32_t kv_it = 0, tile_it = 0, tseq = 0;
       bool ok = true;
 #ifdef INTFA_TIMING
@@ -225,21 +234,20 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const uint64_t descK0 = make_smem_desc(sK, 16, C::SBO_QK, C::SWZ_QK);
       const uint64_t descP0 = make_smem_desc(sP, 16, C::SBO_P, C::SWZ_P);
       const uint64_t descV0 = make_smem_desc(sV, 16, C::SBO_V, C::SWZ_V);
+      // S buffer (it & 1) must be free: the caller has seen P_FULL of step it-2
       auto issue_qk = [&](uint32_t it, bool last) -> bool {
         const uint32_t s = it % NS, ph = (it / NS) & 1;
-        // S must have been copied out and re-armed by the softmax warps (step it-1)
         INTFA_T0();
-        if (!mbar_wait_warp(BAR(B_SFREE), (it & 1) ^ 1, abort_flag, p.status, code_hi | PW_SFREE)) return false;
-        INTFA_T(0);
         if (!mbar_wait_warp(BAR(B_KFULL + s), ph, abort_flag, p.status, code_hi | PW_KF)) return false;
         tc_fence_after();
         INTFA_T(1);
         const uint64_t bd0 = descK0 + (uint64_t)(s * (C::K_BYTES >> 4));
+        const uint32_t tSb = tS + (it & 1) * G;
         if (elect_one()) {
-          umma_f16(tS, descArm, descArm, C::IDESC_ARM_S, 0);
+          umma_f16(tSb, descArm, descArm, C::IDESC_ARM_S, 0);
 #pragma unroll
-          for (int kk = 0; kk < D / 32; ++kk) umma_i8(tS, descQ0 + 2 * kk, bd0 + 2 * kk, C::IDESC_QK, 1);
-          umma_commit(BAR(B_SFULL));
+          for (int kk = 0; kk < D / 32; ++kk) umma_i8(tSb, descQ0 + 2 * kk, bd0 + 2 * kk, C::IDESC_QK, 1);
+          umma_commit(BAR(B_SFULL + (it & 1)));
           if (last) umma_commit(BAR(B_QEMPTY));
         }
         __syncwarp();
@@ -251,23 +259,28 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (tile < 0) break;
         const TileInfo t = decode_tile(p, tile, G);
         if (t.nsteps == 0) continue;
+        INTFA_T0();
         ok = mbar_wait_warp(BAR(B_QFULL), tile_it & 1, abort_flag, p.status, code_hi | PW_QF);
         if (!ok) break;
+        INTFA_T(0);
         ok = issue_qk(kv_it, t.nsteps == 1);
+        if (ok && t.nsteps > 1) ok = issue_qk(kv_it + 1, t.nsteps == 2);
         if (!ok) break;
         for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
           const uint32_t s = kv_it % NS, ph = (kv_it / NS) & 1;
-          if (j + 1 < t.nsteps) {
-            ok = issue_qk(kv_it + 1, j + 2 == t.nsteps);
+          const uint32_t b = kv_it & 1;
+          INTFA_T0();
+          ok = mbar_wait_warp(BAR(B_PFULL + b), (kv_it >> 1) & 1, abort_flag, p.status, code_hi | PW_PFULL);
+          if (!ok) break;
+          INTFA_T(3);
+          // S buffer b is free again: the Q K^T two steps ahead goes first, the softmax group waits for it
+          if (elect_one()) umma_commit(BAR(B_KEMPTY + s));   // K scales of step j have been read as well
+          __syncwarp();
+          if (j + 2 < t.nsteps) {
+            ok = issue_qk(kv_it + 2, j + 3 == t.nsteps);
             if (!ok) break;
           }
           INTFA_T0();
-          ok = mbar_wait_warp(BAR(B_PFULL), kv_it & 1, abort_flag, p.status, code_hi | PW_PFULL);
-          if (!ok) break;
-          INTFA_T(3);
-          // K stage of this step: the K scales in it have been read by the softmax warps (they arrived P)
-          if (elect_one()) umma_commit(BAR(B_KEMPTY + s));
-          __syncwarp();
           ok = mbar_wait_warp(BAR(B_VFULL + s), ph, abort_flag, p.status, code_hi | PW_VF);
           if (!ok) break;
           INTFA_T(4);
@@ -275,7 +288,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           if (!ok) break;
           tc_fence_after();
           INTFA_T(5);
-          const uint64_t ad0 = descP0 + (uint64_t)((kv_it & 1) * (C::P_BYTES >> 4));
+          const uint64_t ad0 = descP0 + (uint64_t)(b * (C::P_BYTES >> 4));
           const uint64_t vd0 = descV0 + (uint64_t)(s * (C::V_BYTES >> 4));
           if (elect_one()) {
             umma_f16(tO, descArm, descArm, C::IDESC_ARM_O, 0);
@@ -283,7 +296,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             for (int kk = 0; kk < G / 32; ++kk) umma_i8(tO, ad0 + 2 * kk, vd0 + kk * ((32 * D) >> 4), C::IDESC_PV, 1);
             umma_commit(BAR(B_OFULL));
             umma_commit(BAR(B_VEMPTY + s));
-            umma_commit(BAR(B_PFREE + (kv_it & 1)));
+            umma_commit(BAR(B_PFREE + b));
           }
           __syncwarp();
           INTFA_T(6);
