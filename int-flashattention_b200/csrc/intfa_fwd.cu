@@ -1,22 +1,26 @@
 // INT8 FlashAttention forward for sm_100a.
 //
-// One CTA owns one 128-row query tile at a time (persistent over a static list of
-// (batch*head, query-block) work items) and walks the KV sequence ASCENDING in tiles
-// of G columns -- G is also the granularity at which the running row maximum is
-// updated, which the full-int8 result depends on (the reference's BLOCK_N,
-// flash_atten_full_int8.py:30-70).
+// Every kernel here gives one CTA one 128-row query tile at a time (work items = (batch*head, query block),
+// drawn from a global counter) and walks the KV sequence ASCENDING in tiles of G columns -- G is also the
+// granularity at which the running row maximum is updated, which the full-int8 result depends on (the
+// reference's BLOCK_N, flash_atten_full_int8.py:30-70).
 //
-// Warp roles (256 threads):
-//   warp 0      TMA producer: Q tile once per work item; K tile, V tile and the K-scale
-//               slice through an NS-stage shared-memory ring (cp.async.bulk.tensor, no multicast)
-//   warp 1      MMA issuer (one thread): S = Q K^T  with tcgen05.mma kind::i8 into an int32
-//               TMEM accumulator; O_j = P V with kind::i8 (full) or kind::f16 (half)
-//   warp 2      TMEM allocator
-//   warps 4-7   softmax/correction/epilogue, one thread per query row: TMEM -> registers,
-//               dequantise with s_q[row]*s_k[col], online softmax, P -> int8 (or fp16) into
-//               swizzled shared memory for the second MMA, then acc = acc*alpha + O_j*s_v/127
-//               in fp32 registers (the int32 PV tile cannot absorb the fp32 rescale, so PV
-//               never accumulates across KV tiles in TMEM).
+// Two kernels share the helpers, the work-item decoding and the arithmetic contract below:
+//   intfa_fwd_pipe_kernel (intfa_fwd_pipe.cuh)  full-int8: one CTA of 640 threads per SM, two softmax
+//               groups on alternate KV steps, separate accumulator warps, double-buffered S in TMEM
+//   intfa_fwd_kernel (this file)                half-int8 (and full-int8 on request): two CTAs of 384
+//               threads per SM:
+//     warp 0      TMA producer: Q tile once per work item; K tile, V tile and the K-scale slice through
+//                 an NS-stage shared-memory ring (cp.async.bulk.tensor, no multicast)
+//     warp 1      MMA issuer (one thread): S = Q K^T with tcgen05.mma kind::i8 into an int32 TMEM
+//                 accumulator; O_j = P V with kind::i8 (full) or kind::f16 (half)
+//     warp 2      TMEM allocator; warp 3 watcher (polls the tensor core's mbarriers, releases the
+//                 softmax warps through named barriers)
+//     warps 4-11  softmax/correction/epilogue, two threads per query row: TMEM -> registers,
+//                 dequantise with s_q[row]*s_k[col], online softmax, P -> int8 (or fp16) into
+//                 swizzled shared memory for the second MMA, then acc = acc*alpha + O_j*s_v/127
+//                 with the fp32 accumulator row in TMEM (the int32 PV tile cannot absorb the fp32
+//                 rescale, so PV never accumulates across KV tiles as int32).
 //
 // Arithmetic contract (what the parity tests pin; reference lines in parentheses):
 //   s   = (fp32(S32) * s_q[row]) * s_k[col]                 (flash_atten_full_int8.py:36-38)
