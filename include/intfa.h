@@ -31,6 +31,9 @@ extern "C" {
 #define INTFA_VARIANT_FULL 0         /* int8 Q/K/V, int8 P  (flash_atten_full_int8.py) */
 #define INTFA_VARIANT_HALF 1         /* int8 Q/K, fp16 V, fp16 P (flash_atten_int8.py)  */
 
+#define INTFA_OUT_FP16 0             /* o as fp16: the Triton ops (flash_atten_full_int8.py:194-195) */
+#define INTFA_OUT_BF16 1             /* o as bf16: csrc/flash_fwd_hdim128_bf16_sm80_{full,half}_qi8.cu */
+
 #define INTFA_VSCALE_PER_TENSOR  0   /* one V scale per (batch, head): benchmark.py:102-107 */
 #define INTFA_VSCALE_PER_CHANNEL 1   /* one V scale per (batch, head, channel)              */
 
@@ -79,6 +82,11 @@ typedef struct IntfaFwdParams {
   int32_t* dbg_s; void* dbg_p; int32_t dbg_tile; int32_t dbg_step;
   int32_t* status;              /* device int32, zeroed by the caller; a device-side wait that runs
                                    out stores a non-zero code here.  May be NULL. */
+  int32_t H_kv;                 /* grouped-query / multi-query attention: number of K/V heads; k, v and
+                                   their scales are [B,H_kv,...], query head h reads K/V head h / (H/H_kv)
+                                   (h_h_k_ratio, csrc/flash.h:60-63, csrc/flash_fwd_kernel_full_qi8.h:141-160).
+                                   0 means H.  H must be a multiple of H_kv. */
+  int32_t o_dtype;              /* INTFA_OUT_*: element type of o (2 bytes either way) */
 } IntfaFwdParams;
 
 /*

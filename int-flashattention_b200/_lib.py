@@ -39,6 +39,7 @@ class IntfaFwdParams(ctypes.Structure):
         ("dbg_s", ctypes.c_void_p), ("dbg_p", ctypes.c_void_p),
         ("dbg_tile", ctypes.c_int32), ("dbg_step", ctypes.c_int32),
         ("status", ctypes.c_void_p),
+        ("H_kv", ctypes.c_int32), ("o_dtype", ctypes.c_int32),
     ]
 
 

@@ -76,6 +76,10 @@ int intfa_fwd(const IntfaFwdParams* p, void* stream) {
   if (p->Nq % 128 != 0) return set_error(INTFA_ERR_UNSUPPORTED, "Nq=%d must be a multiple of 128", p->Nq);
   if (p->Nk % p->G != 0) return set_error(INTFA_ERR_UNSUPPORTED, "Nk=%d must be a multiple of G=%d", p->Nk, p->G);
   if (p->p_round != 0 && p->p_round != 1) return set_error(INTFA_ERR_INVALID_ARG, "p_round must be 0 or 1");
+  if (p->H_kv < 0 || (p->H_kv > 0 && p->H % p->H_kv != 0))
+    return set_error(INTFA_ERR_INVALID_ARG, "H=%d must be a multiple of H_kv=%d", p->H, p->H_kv);
+  if (p->o_dtype != INTFA_OUT_FP16 && p->o_dtype != INTFA_OUT_BF16)
+    return set_error(INTFA_ERR_INVALID_ARG, "o_dtype must be INTFA_OUT_FP16 or INTFA_OUT_BF16");
   if ((long long)p->B * p->H * (p->Nq / 128) > 0x7fffffffLL) return set_error(INTFA_ERR_TOO_LARGE, "too many work items");
   int rc;
   if ((rc = check_tma_tensor("q", p->q, p->q_stride, 1))) return rc;

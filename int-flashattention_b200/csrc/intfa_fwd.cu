@@ -33,6 +33,7 @@
 //   m carried across the off-band/on-band boundary           (flash_atten_int8.py:66,157,166)
 //   o   = fp16(acc / l)                                      (:181-182)
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -113,8 +114,18 @@ struct Cfg {
   static constexpr uint32_t IDESC_PV = FULL ? make_idesc(2, 1, 1, 0, 1, kBM, D) : make_idesc(1, 0, 0, 0, 1, kBM, D);
 };
 
+// two output values as one 32-bit word: fp16 (the Triton ops' output type) or bf16 (the CUDA path's other one)
+__device__ __forceinline__ uint32_t pack_out(float x, float y, int bf16) {
+  if (bf16) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+  const __half2 h = __floats2half2_rn(x, y);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
 struct TileInfo {
-  int bh, b, h, mb, work, nsteps;
+  int bh, b, h, hk, mb, work, nsteps;   // hk: the K/V head this query head reads (grouped-query attention)
 };
 
 __device__ __forceinline__ TileInfo decode_tile(const KParams& p, int tile, int G) {
@@ -124,6 +135,7 @@ __device__ __forceinline__ TileInfo decode_tile(const KParams& p, int tile, int 
   t.mb = p.causal ? (p.MB - 1 - i) : i;       // causal: long rows first
   t.b = t.bh / p.H;
   t.h = t.bh - t.b * p.H;
+  t.hk = t.h / p.hk_ratio;
   t.work = t.bh * p.MB + t.mb;
   int n = p.Nk / G;
   if (p.causal) {
@@ -274,22 +286,22 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (!ok) break;
         mbar_expect_tx(BAR(B_QFULL), C::Q_BYTES);
         tma_load_4d(sQ, &tmQ, BAR(B_QFULL), 0, t.mb * kBM, t.h, t.b);
-        const float* ks_row = p.ks + (long long)t.b * p.ks_sb + (long long)t.h * p.ks_sh;
+        const float* ks_row = p.ks + (long long)t.b * p.ks_sb + (long long)t.hk * p.ks_sh;
         for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
           const uint32_t s = kv_it % NS, ph = (kv_it / NS) & 1;
           ok = mbar_wait<kSleepProducer>(BAR(B_KEMPTY + s), ph ^ 1, abort_flag, p.status, code_hi | W_K_EMPTY);
           if (!ok) break;
           mbar_expect_tx(BAR(B_KFULL + s), C::K_BYTES);
-          tma_load_4d(sK + s * C::K_BYTES, &tmK, BAR(B_KFULL + s), 0, j * G, t.h, t.b);
+          tma_load_4d(sK + s * C::K_BYTES, &tmK, BAR(B_KFULL + s), 0, j * G, t.hk, t.b);
           ok = mbar_wait<kSleepProducer>(BAR(B_VEMPTY + s), ph ^ 1, abort_flag, p.status, code_hi | W_V_EMPTY);
           if (!ok) break;
           mbar_expect_tx(BAR(B_VFULL + s), C::V_BYTES + C::KS_BYTES);
           if constexpr (FULL) {
-            tma_load_4d(sV + s * C::V_BYTES, &tmV, BAR(B_VFULL + s), 0, j * G, t.h, t.b);
+            tma_load_4d(sV + s * C::V_BYTES, &tmV, BAR(B_VFULL + s), 0, j * G, t.hk, t.b);
           } else {
 #pragma unroll
             for (int c = 0; c < D / 64; ++c)
-              tma_load_4d(sV + s * C::V_BYTES + c * (G * 128), &tmV, BAR(B_VFULL + s), c * 64, j * G, t.h, t.b);
+              tma_load_4d(sV + s * C::V_BYTES + c * (G * 128), &tmV, BAR(B_VFULL + s), c * 64, j * G, t.hk, t.b);
           }
           bulk_load_1d(sKS + s * C::KS_BYTES, ks_row + j * G, C::KS_BYTES, BAR(B_VFULL + s));
         }
@@ -478,7 +490,7 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         named_bar_sync(1, kComputeThreads);       // previous work item done with vsd_s
         const int ch = threadIdx.x - 128;
         if (ch < D)
-          vsd_s[ch] = p.vs[(long long)t.b * p.vs_sb + (long long)t.h * p.vs_sh + (long long)ch * p.vs_sd] / 127.0f;
+          vsd_s[ch] = p.vs[(long long)t.b * p.vs_sb + (long long)t.hk * p.vs_sh + (long long)ch * p.vs_sd] / 127.0f;
         named_bar_sync(1, kComputeThreads);
       }
 
@@ -757,9 +769,8 @@ intfa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             uint32_t w[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const __half2 h = __floats2half2_rn(__uint_as_float(a[8 * i + 2 * e]) / l_row,
-                                                  __uint_as_float(a[8 * i + 2 * e + 1]) / l_row);
-              w[e] = *reinterpret_cast<const uint32_t*>(&h);
+              w[e] = pack_out(__uint_as_float(a[8 * i + 2 * e]) / l_row, __uint_as_float(a[8 * i + 2 * e + 1]) / l_row,
+                              p.o_bf16);
             }
             *reinterpret_cast<uint4*>(orow + cc * 32 + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
           }
@@ -863,6 +874,8 @@ static int make_tmap(CUtensorMap* tm, const void* base, int esize, const int64_t
   return INTFA_OK;
 }
 
+static inline int kv_heads(const IntfaFwdParams* a) { return a->H_kv > 0 ? a->H_kv : a->H; }
+
 template <int D, int G, bool FULL, bool PRNE>
 static int launch(const IntfaFwdParams* a, const KParams& kp, cudaStream_t stream) {
   using C = Cfg<D, G, FULL>;
@@ -870,11 +883,11 @@ static int launch(const IntfaFwdParams* a, const KParams& kp, cudaStream_t strea
   const CUtensorMapSwizzle swzD = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   int rc;
   if ((rc = make_tmap(&tmQ, a->q, 1, a->q_stride, a->B, a->H, a->Nq, D, D, kBM, swzD))) return rc;
-  if ((rc = make_tmap(&tmK, a->k, 1, a->k_stride, a->B, a->H, a->Nk, D, D, G, swzD))) return rc;
+  if ((rc = make_tmap(&tmK, a->k, 1, a->k_stride, a->B, kv_heads(a), a->Nk, D, D, G, swzD))) return rc;
   if constexpr (FULL) {
-    if ((rc = make_tmap(&tmV, a->v, 1, a->v_stride, a->B, a->H, a->Nk, D, D, G, swzD))) return rc;
+    if ((rc = make_tmap(&tmV, a->v, 1, a->v_stride, a->B, kv_heads(a), a->Nk, D, D, G, swzD))) return rc;
   } else {
-    if ((rc = make_tmap(&tmV, a->v, 2, a->v_stride, a->B, a->H, a->Nk, D, 64, G, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    if ((rc = make_tmap(&tmV, a->v, 2, a->v_stride, a->B, kv_heads(a), a->Nk, D, 64, G, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   }
   auto kern = intfa_fwd_kernel<D, G, FULL, PRNE>;
   static bool attr_done = false;     // per instantiation; the attribute is per device, so set it every time a device changes
@@ -912,8 +925,8 @@ static int launch_pipe(const IntfaFwdParams* a, const KParams& kp, cudaStream_t 
   const CUtensorMapSwizzle swzD = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   int rc;
   if ((rc = make_tmap(&tmQ, a->q, 1, a->q_stride, a->B, a->H, a->Nq, D, D, kBM, swzD))) return rc;
-  if ((rc = make_tmap(&tmK, a->k, 1, a->k_stride, a->B, a->H, a->Nk, D, D, G, swzD))) return rc;
-  if ((rc = make_tmap(&tmV, a->v, 1, a->v_stride, a->B, a->H, a->Nk, D, D, G, swzD))) return rc;
+  if ((rc = make_tmap(&tmK, a->k, 1, a->k_stride, a->B, kv_heads(a), a->Nk, D, D, G, swzD))) return rc;
+  if ((rc = make_tmap(&tmV, a->v, 1, a->v_stride, a->B, kv_heads(a), a->Nk, D, D, G, swzD))) return rc;
   auto kern = intfa_fwd_pipe_kernel<D, G, PRNE>;
   static bool attr_done = false;
   static int attr_dev = -1;
@@ -946,6 +959,8 @@ int fwd_dispatch(const IntfaFwdParams* a, cudaStream_t stream) {
   kp.ks_sb = a->ks_stride[0]; kp.ks_sh = a->ks_stride[1];
   kp.vs_sb = a->vs_stride[0]; kp.vs_sh = a->vs_stride[1]; kp.vs_sd = a->vs_stride[2];
   kp.B = a->B; kp.H = a->H; kp.Nq = a->Nq; kp.Nk = a->Nk;
+  kp.hk_ratio = a->H / kv_heads(a);
+  kp.o_bf16 = a->o_dtype == INTFA_OUT_BF16 ? 1 : 0;
   kp.causal = a->causal ? 1 : 0;
   kp.c = a->sm_scale * 1.44269504f;          // fp32 product, flash_atten_full_int8.py:156-157
   kp.q_off = a->q_offset; kp.kv_off = a->kv_offset;

@@ -201,18 +201,18 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (!ok) break;
         mbar_expect_tx(BAR(B_QFULL), C::Q_BYTES);
         tma_load_4d(sQ, &tmQ, BAR(B_QFULL), 0, t.mb * kBM, t.h, t.b);
-        const float* ks_row = p.ks + (long long)t.b * p.ks_sb + (long long)t.h * p.ks_sh;
+        const float* ks_row = p.ks + (long long)t.b * p.ks_sb + (long long)t.hk * p.ks_sh;
         for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
           const uint32_t s = kv_it % NS, ph = (kv_it / NS) & 1;
           ok = mbar_wait(BAR(B_KEMPTY + s), ph ^ 1, abort_flag, p.status, code_hi | PW_KE);
           if (!ok) break;
           mbar_expect_tx(BAR(B_KFULL + s), C::K_BYTES + C::KS_BYTES);
-          tma_load_4d(sK + s * C::K_BYTES, &tmK, BAR(B_KFULL + s), 0, j * G, t.h, t.b);
+          tma_load_4d(sK + s * C::K_BYTES, &tmK, BAR(B_KFULL + s), 0, j * G, t.hk, t.b);
           bulk_load_1d(sKS + s * C::KS_BYTES, ks_row + j * G, C::KS_BYTES, BAR(B_KFULL + s));
           ok = mbar_wait(BAR(B_VEMPTY + s), ph ^ 1, abort_flag, p.status, code_hi | PW_VE);
           if (!ok) break;
           mbar_expect_tx(BAR(B_VFULL + s), C::V_BYTES);
-          tma_load_4d(sV + s * C::V_BYTES, &tmV, BAR(B_VFULL + s), 0, j * G, t.h, t.b);
+          tma_load_4d(sV + s * C::V_BYTES, &tmV, BAR(B_VFULL + s), 0, j * G, t.hk, t.b);
         }
         ++tile_it;
       }

@@ -15,6 +15,8 @@ struct KParams {
   long long o_sb, o_sh, o_sn;
   long long qs_sb, qs_sh, ks_sb, ks_sh, vs_sb, vs_sh, vs_sd;
   int B, H, Nq, Nk;
+  int hk_ratio;                  // query heads per K/V head (1 unless grouped-query attention)
+  int o_bf16;                    // output element type: 0 fp16, 1 bf16
   int causal;
   float c;                       // sm_scale * 1.44269504 (fp32)
   long long q_off, kv_off;

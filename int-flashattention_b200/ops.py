@@ -88,7 +88,7 @@ def _scales_f32(s):
 
 def _fwd(variant, q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, *, G=None, p_round="triton",
          state=None, q_offset=0, kv_offset=0, return_state=False, return_lse=False, write_o=True,
-         debug_tap=None):
+         debug_tap=None, out_dtype=torch.float16):
     # shape constraints, as flash_atten_full_int8.py:189-193
     HEAD_DIM_Q, HEAD_DIM_K, HEAD_DIM_V = q.shape[-1], k.shape[-1], v.shape[-1]
     assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V
@@ -104,11 +104,16 @@ def _fwd(variant, q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, *, G=Non
         raise TypeError("half-int8: v must be float16")
     B, H, Nq, D = q.shape
     Nk = k.shape[2]
+    H_kv = k.shape[1]                          # grouped-query attention: fewer K/V heads than query heads
+    if v.shape[1] != H_kv or H % H_kv != 0:
+        raise ValueError("k and v must have the same number of heads, dividing the %d query heads" % H)
+    if out_dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("out_dtype must be torch.float16 or torch.bfloat16")
     if G is None:
         G = default_G(D, variant)
     q, k, v = _prep_main(q), _prep_main(k), _prep_main(v)
     qs, ks = _scales_f32(q_scale), _scales_f32(k_scale)
-    o = torch.empty((B, H, Nq, D) if write_o else (1, 1, 1, 8), dtype=torch.float16, device=q.device)  # :194-195
+    o = torch.empty((B, H, Nq, D) if write_o else (1, 1, 1, 8), dtype=out_dtype, device=q.device)  # :194-195
 
     P = _lib.IntfaFwdParams()
     P.q, P.k, P.v, P.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
@@ -133,6 +138,8 @@ def _fwd(variant, q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, *, G=Non
         P.v_scale = vs.data_ptr()
         keep.append(vs)
     P.B, P.H, P.Nq, P.Nk, P.D = B, H, Nq, Nk, D
+    P.H_kv = H_kv
+    P.o_dtype = 1 if out_dtype == torch.bfloat16 else 0
     P.variant = _lib.VARIANT_FULL if full else _lib.VARIANT_HALF
     P.causal = 1 if causal else 0
     P.sm_scale = float(sm_scale)
@@ -185,7 +192,8 @@ def attention_full_int8(q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, **
     full-int8 Triton kernel drops it (flash_atten_full_int8.py:71,166-179).
     Extra keyword arguments (not in the reference): G (running-max granularity, the reference's
     BLOCK_N), p_round ("triton" | "rne"), state/q_offset/kv_offset/return_state (ring attention),
-    return_lse, debug_tap."""
+    return_lse, debug_tap, out_dtype (torch.float16 | torch.bfloat16).  k, v and their scales may have
+    fewer heads than q (grouped-query attention: query head h reads K/V head h // (H // H_kv))."""
     return _fwd("full", q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, **kw)
 
 

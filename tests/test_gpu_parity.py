@@ -335,5 +335,59 @@ def test_full_size_half_int8_causal(pkg, oracle, dev):
     _full_size(pkg, oracle, dev, 8, 32, 4096, 128, "half", True, 1002, True, [(0, 0), (7, 13)])
 
 
+# --------------------------------------------------- the CUDA path's surface: grouped heads, bf16 output
+@pytest.mark.parametrize("variant,causal", [("full", False), ("full", True), ("half", True)])
+def test_grouped_query_heads(variant, causal, pkg, oracle, dev):
+    """Fewer K/V heads than query heads: query head h reads K/V head h // (H // H_kv)
+    (csrc/flash_fwd_kernel_full_qi8.h:141-160).  The oracle sees the K/V heads repeated."""
+    B, H, Hk, N, D = 2, 8, 2, 512, 128
+    q, _, _ = make_qkv(61, B, H, N, D)
+    _, k, v = make_qkv(62, B, Hk, N, D)
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    rep = H // Hk
+    sm = D ** -0.5
+    if variant == "full":
+        v8, vs = oracle.quant_perchannel(v)
+        ref = oracle.attention_full_int8(q8, k8.repeat_interleave(rep, 1), v8.repeat_interleave(rep, 1), qs,
+                                         ks.repeat_interleave(rep, 1), vs.repeat_interleave(rep, 1), causal, sm)
+        out = pkg.attention_full_int8(q8.to(dev), k8.to(dev), v8.to(dev), qs.to(dev), ks.to(dev), vs.to(dev), causal, sm)
+    else:
+        ref = oracle.attention_int8(q8, k8.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1), qs,
+                                    ks.repeat_interleave(rep, 1), causal, sm, G=64)
+        out = pkg.attention_int8(q8.to(dev), k8.to(dev), v.to(dev), qs.to(dev), ks.to(dev), causal, sm)
+    pkg.check_status()
+    assert out.shape == (B, H, N, D)
+    _close(oracle, out, ref)
+    with pytest.raises(ValueError):
+        pkg.attention_full_int8(q8.to(dev), k8[:, :1].repeat(1, 3, 1, 1).to(dev), k8[:, :1].repeat(1, 3, 1, 1).to(dev),
+                                qs.to(dev), ks[:, :1].repeat(1, 3, 1).to(dev), torch.ones(B, 3, device=dev), causal, sm)
+
+
+@pytest.mark.parametrize("variant", ["full", "half"])
+def test_bf16_output(variant, pkg, oracle, dev):
+    """o as bf16 (csrc/flash_fwd_hdim128_bf16_sm80_{full,half}_qi8.cu): the same fp32 acc/l, rounded to bf16."""
+    B, H, N, D = 1, 4, 512, 128
+    q, k, v = make_qkv(63, B, H, N, D)
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    sm = D ** -0.5
+    if variant == "full":
+        v8, vs = oracle.quant_perchannel(v)
+        args = (q8.to(dev), k8.to(dev), v8.to(dev), qs.to(dev), ks.to(dev), vs.to(dev), True, sm)
+        f = pkg.attention_full_int8
+    else:
+        args = (q8.to(dev), k8.to(dev), v.to(dev), qs.to(dev), ks.to(dev), True, sm)
+        f = pkg.attention_int8
+    o16 = f(*args)
+    ob = f(*args, out_dtype=torch.bfloat16)
+    pkg.check_status()
+    assert ob.dtype == torch.bfloat16 and ob.shape == o16.shape
+    # both are roundings of the same fp32 value: they differ by at most half a bf16 ulp plus half an fp16 ulp
+    d = (ob.float() - o16.float()).abs()
+    assert bool((d <= o16.float().abs() * (2.0 ** -8 + 2.0 ** -11) + 1e-7).all())
+    assert float(d.max()) > 0.0                       # and it is not simply the fp16 result again
+
+
 def test_status_word_clean(pkg, dev):
     assert pkg.check_status(dev) == 0
