@@ -240,7 +240,7 @@ def run_ring(args, pkg, dist, rank, world, local_rank, dev):
                            "half_chunk_rows": nh, "bytes_per_half_chunk_transfer": kv_bytes,
                            "l2": "inputs exceed L2"},
                 "clocks": clocks, "gpu_launches": steps * (5 + 2 * world + 1),
-                "roofline": {"bound": "tensor", "kernel": "intfa_fwd_pipe_kernel" if variant == "full" else "intfa_fwd_kernel",
+                "roofline": {"bound": "tensor", "kernel": "intfa_fwd_pipe_kernel" if (variant == "full" or D == 128) else "intfa_fwd_kernel",
                              "achieved": value / world,
                              "peak": 2.0 * peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                              "frac": value / world / (2.0 * peaks["bf16_tflops_sustained"]), "traffic": None,
@@ -374,7 +374,7 @@ def main():
         pj = os.path.join(ROOT, "profiles", "roofline_inputs.json")
         if os.path.exists(pj):
             prof = json.load(open(pj)).get(args.workload, {})
-        roofline = {"bound": "tensor", "kernel": "intfa_fwd_pipe_kernel" if full else "intfa_fwd_kernel",
+        roofline = {"bound": "tensor", "kernel": "intfa_fwd_pipe_kernel" if (full or D == 128) else "intfa_fwd_kernel",
                     "achieved": achieved, "peak": peak_int8,
                     "unit": "TFLOP/s", "frac": achieved / peak_int8,
                     "traffic": prof.get("attn_dram_bytes_per_launch"),

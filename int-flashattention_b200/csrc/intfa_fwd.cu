@@ -6,10 +6,11 @@
 // reference's BLOCK_N, flash_atten_full_int8.py:30-70).
 //
 // Two kernels share the helpers, the work-item decoding and the arithmetic contract below:
-//   intfa_fwd_pipe_kernel (intfa_fwd_pipe.cuh)  full-int8: one CTA of 640 threads per SM, two softmax
-//               groups on alternate KV steps, separate accumulator warps, double-buffered S in TMEM
-//   intfa_fwd_kernel (this file)                half-int8 (and full-int8 on request): two CTAs of 384
-//               threads per SM:
+//   intfa_fwd_pipe_kernel (intfa_fwd_pipe.cuh)  full-int8, and half-int8 at head_dim 128: one CTA of 640
+//               threads per SM, two softmax groups on alternate KV steps, separate accumulator warps,
+//               double-buffered S in TMEM
+//   intfa_fwd_kernel (this file)                half-int8 at head_dim 64 (and everything on request): two
+//               CTAs of 384 threads per SM:
 //     warp 0      TMA producer: Q tile once per work item; K tile, V tile and the K-scale slice through
 //                 an NS-stage shared-memory ring (cp.async.bulk.tensor, no multicast)
 //     warp 1      MMA issuer (one thread): S = Q K^T with tcgen05.mma kind::i8 into an int32 TMEM
@@ -917,17 +918,21 @@ static int launch(const IntfaFwdParams* a, const KParams& kp, cudaStream_t strea
 }
 
 // Pipelined full-int8 kernel: one CTA per SM.
-template <int D, int G, bool PRNE>
+template <int D, int G, bool FULL, bool PRNE>
 static int launch_pipe(const IntfaFwdParams* a, const KParams& kp, cudaStream_t stream) {
-  using C = PipeCfg<D, G>;
+  using C = PipeCfg<D, G, FULL>;
   static_assert(C::SMEM_BYTES <= 227 * 1024, "shared memory");
   CUtensorMap tmQ, tmK, tmV;
   const CUtensorMapSwizzle swzD = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   int rc;
   if ((rc = make_tmap(&tmQ, a->q, 1, a->q_stride, a->B, a->H, a->Nq, D, D, kBM, swzD))) return rc;
   if ((rc = make_tmap(&tmK, a->k, 1, a->k_stride, a->B, kv_heads(a), a->Nk, D, D, G, swzD))) return rc;
-  if ((rc = make_tmap(&tmV, a->v, 1, a->v_stride, a->B, kv_heads(a), a->Nk, D, D, G, swzD))) return rc;
-  auto kern = intfa_fwd_pipe_kernel<D, G, PRNE>;
+  if constexpr (FULL) {
+    if ((rc = make_tmap(&tmV, a->v, 1, a->v_stride, a->B, kv_heads(a), a->Nk, D, D, G, swzD))) return rc;
+  } else {
+    if ((rc = make_tmap(&tmV, a->v, 2, a->v_stride, a->B, kv_heads(a), a->Nk, D, 64, G, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  }
+  auto kern = intfa_fwd_pipe_kernel<D, G, FULL, PRNE>;
   static bool attr_done = false;
   static int attr_dev = -1;
   int dev = 0;
@@ -973,11 +978,14 @@ int fwd_dispatch(const IntfaFwdParams* a, cudaStream_t stream) {
   const bool full = a->variant == INTFA_VARIANT_FULL;
   const bool rne = full && a->p_round == 1;
   const int D = a->D, G = a->G;
+  // The one-CTA pipelined kernel serves full-int8 and half-int8 at head_dim 128; half-int8 at head_dim 64 is
+  // faster on the two-CTA kernel (measured), which INTFA_LEGACY_KERNEL in the environment selects for everything.
   static const bool use_pipe = getenv("INTFA_LEGACY_KERNEL") == nullptr;
 #define INTFA_CASE(DD, GG)                                                       \
   if (D == DD && G == GG) {                                                      \
-    if (full && use_pipe) return rne ? launch_pipe<DD, GG, true>(a, kp, stream)  \
-                                     : launch_pipe<DD, GG, false>(a, kp, stream);\
+    if (full && use_pipe) return rne ? launch_pipe<DD, GG, true, true>(a, kp, stream)  \
+                                     : launch_pipe<DD, GG, true, false>(a, kp, stream);\
+    if (use_pipe && DD == 128) return launch_pipe<DD, GG, false, false>(a, kp, stream); \
     if (full) return rne ? launch<DD, GG, true, true>(a, kp, stream)             \
                          : launch<DD, GG, true, false>(a, kp, stream);           \
     return launch<DD, GG, false, false>(a, kp, stream);                          \

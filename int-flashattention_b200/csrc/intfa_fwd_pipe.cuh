@@ -1,4 +1,4 @@
-// Full-int8 attention forward, pipelined variant: ONE CTA per SM, one 128-row query tile at a time.
+// INT8 attention forward, pipelined kernel (full-int8 and half-int8): ONE CTA per SM, one 128-row query tile at a time.
 // (Included by intfa_fwd.cu inside namespace intfa, after the shared helpers.)
 //
 // 640 threads:
@@ -12,8 +12,10 @@
 //                 MUFU).  The running max m and row sum l of a row travel between the two threads that own
 //                 it through shared memory, once per step each.
 //   warps 12-19   accumulator update and epilogue, two threads per query row (half the channels each):
-//                 acc = acc*alpha + fp32(O_j)*s_v/127 with acc (fp32) and O_j (int32) both in TMEM.
-// TMEM columns: S0 [0,G) | S1 [G,2G) | O_j [2G, 2G+D) | acc [2G+D, 2G+2D)  (<= 512).
+//                 full-int8: acc = acc*alpha + fp32(O_j)*s_v/127 with acc (fp32) and O_j (int32) both in TMEM;
+//                 half-int8: P V (fp16 MMA) accumulates straight into acc, these warps multiply the row by
+//                 alpha beforehand when some alpha of the warp's 32 rows is not 1.
+// TMEM columns: S0 [0,G) | S1 [G,2G) | O_j [2G, 2G+D) | acc [2G+D, 2G+2D)  (<= 512); half-int8: no O_j, acc at 2G.
 // S and O_j are int32 accumulators that start each KV step from the bit pattern of 1.5*2^23, written by a
 // small fp16 MMA ahead of the int8 MMAs, so that the threads read fp32(S32) + 1.5*2^23 without a conversion.
 // Arithmetic is the same as in intfa_fwd_kernel (see the contract at the top of intfa_fwd.cu).
@@ -29,14 +31,14 @@ constexpr int kPipeServiceRegs = 40, kPipeSoftmaxRegs = 128, kPipeCorrRegs = 80;
 static_assert(128 * kPipeServiceRegs + kPipeSoftmaxThreads * kPipeSoftmaxRegs + kPipeCorrThreads * kPipeCorrRegs <=
                   kPipeThreads * kPipeLaunchRegs, "setmaxnreg budget exceeds the registers the CTA is launched with");
 
-template <int D, int G>
+template <int D, int G, bool FULL>
 struct PipeCfg {
   static constexpr int Q_BYTES = kBM * D;
   static constexpr int K_BYTES = G * D;
-  static constexpr int V_BYTES = G * D;
-  static constexpr int P_BYTES = kBM * G;
+  static constexpr int V_BYTES = FULL ? G * D : G * D * 2;         // int8, or fp16 as D/64 boxes of [G keys][64 channels]
+  static constexpr int P_BYTES = FULL ? kBM * G : kBM * G * 2;     // int8, or fp16 as G/64 blocks of [128 rows][64 columns]
   static constexpr int KS_BYTES = G * 4;
-  static constexpr int NS = 4;
+  static constexpr int NS = (FULL || G == 64) ? 4 : 2;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
   static constexpr int OFF_V = OFF_K + NS * K_BYTES;
@@ -50,32 +52,32 @@ struct PipeCfg {
   static constexpr int OFF_MAGIC = OFF_FIN + 2 * 128 * 8;          // 4 KB constant fp16 operand of the "arm" MMA
   static constexpr int MAGIC_BYTES = 4096;
   static constexpr int OFF_BAR = OFF_MAGIC + MAGIC_BYTES;
-  static constexpr int NUM_BARS = 17 + 4 * NS + 8;
+  static constexpr int NUM_BARS = 17 + 4 * NS + 8 + 4;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 32 + 1024;
-  static constexpr int COL_S = 0, COL_O = 2 * G, COL_ACC = 2 * G + D;   // S buffer b at COL_S + b*G
+  static constexpr int COL_S = 0, COL_O = 2 * G, COL_ACC = FULL ? 2 * G + D : 2 * G;   // S buffer b at COL_S + b*G; no O_j for half-int8
   static constexpr int TMEM_COLS = 512;
   static constexpr uint64_t SWZ_QK = (D == 128) ? kSwz128 : kSwz64;
   static constexpr uint32_t SBO_QK = 8 * D;
-  static constexpr uint64_t SWZ_P = (G == 128) ? kSwz128 : kSwz64;
-  static constexpr uint32_t SBO_P = 8 * G;
-  static constexpr uint64_t SWZ_V = (D == 128) ? kSwz128 : kSwz64;
-  static constexpr uint32_t SBO_V = 8 * D;
+  static constexpr uint64_t SWZ_P = FULL ? ((G == 128) ? kSwz128 : kSwz64) : kSwz128;
+  static constexpr uint32_t SBO_P = FULL ? 8 * G : 1024;
+  static constexpr uint64_t SWZ_V = FULL ? ((D == 128) ? kSwz128 : kSwz64) : kSwz128;
+  static constexpr uint32_t SBO_V = FULL ? 8 * D : 1024;
   static constexpr uint32_t IDESC_QK = make_idesc(2, 1, 1, 0, 0, kBM, G);
-  static constexpr uint32_t IDESC_PV = make_idesc(2, 1, 1, 0, 1, kBM, D);
+  static constexpr uint32_t IDESC_PV = FULL ? make_idesc(2, 1, 1, 0, 1, kBM, D) : make_idesc(1, 0, 0, 0, 1, kBM, D);
   // fp16 x fp16 -> fp32, K = 16: writes the fp32 constant 1.5*2^23 into a whole accumulator tile
   static constexpr uint32_t IDESC_ARM_S = make_idesc(1, 0, 0, 0, 0, kBM, G);
   static constexpr uint32_t IDESC_ARM_O = make_idesc(1, 0, 0, 0, 0, kBM, D);
 };
 
 enum PipeWait { PW_TILE = 32, PW_QE, PW_KE, PW_VE, PW_QF, PW_KF, PW_VF, PW_SFREE, PW_PFULL, PW_OFREE, PW_SFULL,
-                PW_PFREE, PW_OFULL, PW_FIN, PW_FINFREE, PW_HM, PW_HL };
+                PW_PFREE, PW_OFULL, PW_FIN, PW_FINFREE, PW_HM, PW_HL, PW_AFULL };
 
-template <int D, int G, bool PRNE>
+template <int D, int G, bool FULL, bool PRNE>
 __global__ void __launch_bounds__(kPipeThreads, 1)
 intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const KParams p) {
-  using C = PipeCfg<D, G>;
+  using C = PipeCfg<D, G, FULL>;
   constexpr int NS = C::NS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -98,6 +100,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   constexpr int B_HL = 15;        // [2] softmax group g (4 warps): row sum after its step published
   constexpr int B_KFULL = 17, B_KEMPTY = 17 + NS, B_VFULL = 17 + 2 * NS, B_VEMPTY = 17 + 3 * NS;
   constexpr int B_TILE = 17 + 4 * NS, B_TDONE = B_TILE + 4;
+  constexpr int B_AFULL = B_TDONE + 4;   // [4] half-int8: alpha of step j (slot j mod 4) published, for the accumulator warps
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 4);
   volatile int* tile_slot = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 16);
@@ -125,6 +128,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     for (int i = 0; i < 4; ++i) {
       mbar_init(BAR(B_TILE + i), 1);
       mbar_init(BAR(B_TDONE + i), 17);       // MMA warp + 8 softmax warps + 8 updater warps
+      mbar_init(BAR(B_AFULL + i), 4);
     }
     *abort_flag = 0;
     mbar_init_fence();
@@ -212,7 +216,13 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           ok = mbar_wait(BAR(B_VEMPTY + s), ph ^ 1, abort_flag, p.status, code_hi | PW_VE);
           if (!ok) break;
           mbar_expect_tx(BAR(B_VFULL + s), C::V_BYTES);
-          tma_load_4d(sV + s * C::V_BYTES, &tmV, BAR(B_VFULL + s), 0, j * G, t.hk, t.b);
+          if constexpr (FULL) {
+            tma_load_4d(sV + s * C::V_BYTES, &tmV, BAR(B_VFULL + s), 0, j * G, t.hk, t.b);
+          } else {
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c)
+              tma_load_4d(sV + s * C::V_BYTES + c * (G * 128), &tmV, BAR(B_VFULL + s), c * 64, j * G, t.hk, t.b);
+          }
         }
         ++tile_it;
       }
@@ -233,7 +243,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const uint64_t descQ0 = make_smem_desc(sQ, 16, C::SBO_QK, C::SWZ_QK);
       const uint64_t descK0 = make_smem_desc(sK, 16, C::SBO_QK, C::SWZ_QK);
       const uint64_t descP0 = make_smem_desc(sP, 16, C::SBO_P, C::SWZ_P);
-      const uint64_t descV0 = make_smem_desc(sV, 16, C::SBO_V, C::SWZ_V);
+      const uint64_t descV0 = make_smem_desc(sV, FULL ? 16 : G * 128, C::SBO_V, C::SWZ_V);
       // S buffer (it & 1) must be free: the caller has seen P_FULL of step it-2
       auto issue_qk = [&](uint32_t it, bool last) -> bool {
         const uint32_t s = it % NS, ph = (it / NS) & 1;
@@ -284,16 +294,28 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           ok = mbar_wait_warp(BAR(B_VFULL + s), ph, abort_flag, p.status, code_hi | PW_VF);
           if (!ok) break;
           INTFA_T(4);
-          ok = mbar_wait_warp(BAR(B_OFREE), (kv_it & 1) ^ 1, abort_flag, p.status, code_hi | PW_OFREE);
+          // full-int8: O_j of the previous step has been read out; half-int8: the accumulator has been brought to
+          // this step's running max (and the previous P V has landed in it)
+          ok = mbar_wait_warp(BAR(B_OFREE), FULL ? ((kv_it & 1) ^ 1) : (kv_it & 1), abort_flag, p.status, code_hi | PW_OFREE);
           if (!ok) break;
           tc_fence_after();
           INTFA_T(5);
           const uint64_t ad0 = descP0 + (uint64_t)(b * (C::P_BYTES >> 4));
           const uint64_t vd0 = descV0 + (uint64_t)(s * (C::V_BYTES >> 4));
           if (elect_one()) {
-            umma_f16(tO, descArm, descArm, C::IDESC_ARM_O, 0);
+            if constexpr (FULL) {
+              umma_f16(tO, descArm, descArm, C::IDESC_ARM_O, 0);
 #pragma unroll
-            for (int kk = 0; kk < G / 32; ++kk) umma_i8(tO, ad0 + 2 * kk, vd0 + kk * ((32 * D) >> 4), C::IDESC_PV, 1);
+              for (int kk = 0; kk < G / 32; ++kk) umma_i8(tO, ad0 + 2 * kk, vd0 + kk * ((32 * D) >> 4), C::IDESC_PV, 1);
+            } else {
+              // fp16 P (K-major, 64-column blocks of 128-byte rows) x fp16 V (MN-major), fp32 accumulate straight
+              // into the accumulator; the first P V of a fresh work item overwrites it
+              const uint32_t keep = (j > 0 || p.state_in) ? 1u : 0u;
+#pragma unroll
+              for (int kk = 0; kk < G / 16; ++kk)
+                umma_f16(tA, ad0 + (uint64_t)((kk >> 2) * ((kBM * 128) >> 4) + (kk & 3) * 2), vd0 + (uint64_t)(kk * (2048 >> 4)),
+                         C::IDESC_PV, kk > 0 ? 1u : keep);
+            }
             umma_commit(BAR(B_OFULL));
             umma_commit(BAR(B_VEMPTY + s));
             umma_commit(BAR(B_PFREE + b));
