@@ -70,7 +70,7 @@ __device__ __forceinline__ void st_stream(void* p, uint2 v) {
 
 constexpr int kQuantUnroll = 4;    // independent 128-bit loads in flight per lane
 
-template <int D>
+template <int D, bool CONTIG>
 __global__ void __launch_bounds__(256) quant_pertoken_kernel(const __half* __restrict__ x, long long sB, long long sH,
                                                              long long sN, int8_t* __restrict__ x8,
                                                              float* __restrict__ scale, int H, int N,
@@ -90,10 +90,16 @@ __global__ void __launch_bounds__(256) quant_pertoken_kernel(const __half* __res
       rows[u] = row;
       v[u] = make_uint4(0, 0, 0, 0);
       if (row < total_rows) {
-        const long long bh = row / N;
-        const int n = (int)(row - bh * N);
-        const int b = (int)(bh / H), h = (int)(bh - (long long)b * H);
-        v[u] = ld_stream(x + b * sB + h * sH + n * sN + sub * 8);
+        if (CONTIG) {
+          v[u] = ld_stream(x + row * D + sub * 8);          // [B,H,N,D] contiguous: the row index is the address
+        } else {
+          // total_rows < 2^31 (checked by the host): 32-bit divisions
+          const unsigned int r32 = (unsigned int)row;
+          const unsigned int bh = r32 / (unsigned int)N;
+          const unsigned int n = r32 - bh * (unsigned int)N;
+          const unsigned int b = bh / (unsigned int)H, h = bh - b * (unsigned int)H;
+          v[u] = ld_stream(x + (long long)b * sB + (long long)h * sH + (long long)n * sN + sub * 8);
+        }
       }
     }
 #pragma unroll
@@ -244,10 +250,16 @@ int quant_pertoken(const void* x, const int64_t* st, void* x8, float* scale, int
   const int rpw = 32 / (D / 8) * kQuantUnroll;
   long long want = (rows + 8LL * rpw - 1) / (8LL * rpw);          // CTAs of 8 warps, one row group each
   const int grid = (int)(want < (long long)sms * 8 ? (want < 1 ? 1 : want) : (long long)sms * 8);
-  if (D == 128)
-    quant_pertoken_kernel<128><<<grid, 256, 0, stream>>>((const __half*)x, st[0], st[1], st[2], (int8_t*)x8, scale, H, N, rows);
-  else
-    quant_pertoken_kernel<64><<<grid, 256, 0, stream>>>((const __half*)x, st[0], st[1], st[2], (int8_t*)x8, scale, H, N, rows);
+  if (rows >= (1LL << 31)) return set_error(INTFA_ERR_TOO_LARGE, "quant_pertoken: B*H*N must be below 2^31");
+  const bool contig = st[2] == D && st[1] == (int64_t)N * D && st[0] == (int64_t)H * N * D;
+#define INTFA_QPT(DD, CC) \
+  quant_pertoken_kernel<DD, CC><<<grid, 256, 0, stream>>>((const __half*)x, st[0], st[1], st[2], (int8_t*)x8, scale, H, N, rows)
+  if (D == 128) {
+    if (contig) INTFA_QPT(128, true); else INTFA_QPT(128, false);
+  } else {
+    if (contig) INTFA_QPT(64, true); else INTFA_QPT(64, false);
+  }
+#undef INTFA_QPT
   return check_launch("quant_pertoken");
 }
 

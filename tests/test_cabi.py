@@ -76,6 +76,14 @@ def test_validation_rejects_before_launch(lib):
     assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_UNSUPPORTED       # G must be 64 or 128
     P.D, P.G = 128, 128
     assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_INVALID_ARG       # q is NULL
+    P.H, P.H_kv = 8, 3
+    assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_INVALID_ARG       # query heads not a multiple of K/V heads
+    assert "H_kv" in lib.last_error()
+    P.H_kv = 2
+    P.o_dtype = 5
+    assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_INVALID_ARG       # unknown output type
+    assert "o_dtype" in lib.last_error()
+    P.o_dtype = 0
     P.variant = 7
     assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_INVALID_ARG
     assert h.intfa_quant_pertoken(None, None, None, None, 1, 1, 1, 128, None) == lib.ERR_INVALID_ARG
