@@ -389,5 +389,22 @@ def test_bf16_output(variant, pkg, oracle, dev):
     assert float(d.max()) > 0.0                       # and it is not simply the fp16 result again
 
 
+def test_host_pipeline_matches_direct_calls(pkg, dev):
+    """HostPipeline (host tensors in, host tensor out, copies overlapped with the kernels) returns exactly
+    what int_flash_attention returns for each submission, in order, also when buffer slots are reused."""
+    B, H, N, D = 1, 4, 512, 128
+    pipe = pkg.HostPipeline((B, H, N, D), dev, causal=True, variant="full", depth=2)
+    ins, outs = [], []
+    for i in range(5):
+        q, k, v = make_qkv(70 + i, B, H, N, D)
+        ins.append(tuple(t.pin_memory() for t in (q, k, v)))
+        outs.append(torch.empty(B, H, N, D, dtype=torch.float16).pin_memory())
+        pipe.submit(*ins[-1], outs[-1])
+    pipe.synchronize()
+    for (q, k, v), o in zip(ins, outs):
+        ref = pkg.int_flash_attention(q.to(dev), k.to(dev), v.to(dev), True, D ** -0.5, variant="full")
+        assert torch.equal(ref.cpu(), o)
+
+
 def test_status_word_clean(pkg, dev):
     assert pkg.check_status(dev) == 0
