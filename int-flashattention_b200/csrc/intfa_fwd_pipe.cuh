@@ -52,7 +52,7 @@ struct PipeCfg {
   static constexpr int OFF_MAGIC = OFF_FIN + 2 * 128 * 8;          // 4 KB constant fp16 operand of the "arm" MMA
   static constexpr int MAGIC_BYTES = 4096;
   static constexpr int OFF_BAR = OFF_MAGIC + MAGIC_BYTES;
-  static constexpr int NUM_BARS = 17 + 4 * NS + 8 + 4;
+  static constexpr int NUM_BARS = 18 + 4 * NS + 8 + 4;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 32 + 1024;
   static constexpr int COL_S = 0, COL_O = 2 * G, COL_ACC = FULL ? 2 * G + D : 2 * G;   // S buffer b at COL_S + b*G; no O_j for half-int8
@@ -94,12 +94,14 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   constexpr int B_PFREE = 6;      // [2] commit: the P V that read P buffer b is done
   constexpr int B_OFULL = 8;      // commit: O_j = P V in TMEM
   constexpr int B_OFREE = 9;      // updater (8 warps): O_j read out
-  constexpr int B_FIN = 10;       // softmax (4 warps of one group): final (m, l) of the work item published
-  constexpr int B_FINFREE = 11;   // [2] updater (8 warps): it has read them
-  constexpr int B_HM = 13;        // [2] softmax group g (4 warps): running max after its step published
-  constexpr int B_HL = 15;        // [2] softmax group g (4 warps): row sum after its step published
-  constexpr int B_KFULL = 17, B_KEMPTY = 17 + NS, B_VFULL = 17 + 2 * NS, B_VEMPTY = 17 + 3 * NS;
-  constexpr int B_TILE = 17 + 4 * NS, B_TDONE = B_TILE + 4;
+  constexpr int B_FIN = 10;       // [2] softmax (4 warps of one group): final (m, l) of the work item published; one
+                                  //     barrier per slot, so that a short next work item cannot complete it twice
+                                  //     before a slow accumulator warp has waited for the first completion
+  constexpr int B_FINFREE = 12;   // [2] updater (8 warps): it has read them
+  constexpr int B_HM = 14;        // [2] softmax group g (4 warps): running max after its step published
+  constexpr int B_HL = 16;        // [2] softmax group g (4 warps): row sum after its step published
+  constexpr int B_KFULL = 18, B_KEMPTY = 18 + NS, B_VFULL = 18 + 2 * NS, B_VEMPTY = 18 + 3 * NS;
+  constexpr int B_TILE = 18 + 4 * NS, B_TDONE = B_TILE + 4;
   constexpr int B_AFULL = B_TDONE + 4;   // [4] half-int8: alpha of step j (slot j mod 4) published, for the accumulator warps
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 4);
@@ -115,10 +117,10 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       mbar_init(BAR(B_FINFREE + b), 8);
       mbar_init(BAR(B_HM + b), 4);
       mbar_init(BAR(B_HL + b), 4);
+      mbar_init(BAR(B_FIN + b), 4);
     }
     mbar_init(BAR(B_OFULL), 1);
     mbar_init(BAR(B_OFREE), 8);
-    mbar_init(BAR(B_FIN), 4);
     for (int s = 0; s < NS; ++s) {
       mbar_init(BAR(B_KFULL + s), 1);
       mbar_init(BAR(B_KEMPTY + s), 1);
