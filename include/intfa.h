@@ -61,7 +61,10 @@ typedef struct IntfaFwdParams {
   const float* q_scale;  const float* k_scale;  const float* v_scale;
   int64_t q_stride[3];  int64_t k_stride[3];  int64_t v_stride[3];  int64_t o_stride[3];
   int64_t qs_stride[2]; int64_t ks_stride[2]; int64_t vs_stride[3];
-  int32_t B, H, Nq, Nk, D;      /* D in {64,128}; Nq multiple of 128; Nk multiple of G */
+  int32_t B, H, Nq, Nk, D;      /* D in {64,128}.  Nq, Nk need not be multiples of the tile sizes (128 rows, G
+                                   columns): the last tiles are masked (csrc/mask.h:277-285); but every row of
+                                   k_scale must be ALLOCATED up to the next multiple of G floats (the values past
+                                   Nk are ignored) -- the scales of a KV step are fetched G at a time */
   int32_t variant;              /* INTFA_VARIANT_* */
   int32_t causal;               /* 0/1; mask is (kv_offset + col) <= (q_offset + row) */
   float   sm_scale;             /* natural-log softmax scale; kernel multiplies by 1.44269504 */

@@ -73,8 +73,6 @@ int intfa_fwd(const IntfaFwdParams* p, void* stream) {
   if (p->D != 64 && p->D != 128)
     return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: the sm_100a kernels cover 64 and 128", p->D);
   if (p->G != 64 && p->G != 128) return set_error(INTFA_ERR_UNSUPPORTED, "G=%d unsupported: 64 or 128", p->G);
-  if (p->Nq % 128 != 0) return set_error(INTFA_ERR_UNSUPPORTED, "Nq=%d must be a multiple of 128", p->Nq);
-  if (p->Nk % p->G != 0) return set_error(INTFA_ERR_UNSUPPORTED, "Nk=%d must be a multiple of G=%d", p->Nk, p->G);
   if (p->p_round != 0 && p->p_round != 1) return set_error(INTFA_ERR_INVALID_ARG, "p_round must be 0 or 1");
   if (p->H_kv < 0 || (p->H_kv > 0 && p->H % p->H_kv != 0))
     return set_error(INTFA_ERR_INVALID_ARG, "H=%d must be a multiple of H_kv=%d", p->H, p->H_kv);
@@ -88,6 +86,13 @@ int intfa_fwd(const IntfaFwdParams* p, void* stream) {
   if (!p->q_scale || !p->k_scale) return set_error(INTFA_ERR_INVALID_ARG, "q_scale / k_scale is NULL");
   if (!aligned16(p->k_scale) || p->ks_stride[0] % 4 != 0 || p->ks_stride[1] % 4 != 0)
     return set_error(INTFA_ERR_INVALID_ARG, "k_scale must be 16-byte aligned with (B,H) strides that are multiples of 4");
+  {
+    // the K scales of a KV step are fetched G at a time: every row must have room up to the next multiple of G
+    const long long need = ((long long)p->Nk + p->G - 1) / p->G * p->G;
+    const int hk = p->H_kv > 0 ? p->H_kv : p->H;
+    if ((hk > 1 && p->ks_stride[1] < need) || (p->B > 1 && p->ks_stride[0] < need * hk))
+      return set_error(INTFA_ERR_INVALID_ARG, "k_scale rows must be allocated up to the next multiple of G (%lld floats for Nk=%d)", need, p->Nk);
+  }
   if (full && !p->v_scale) return set_error(INTFA_ERR_INVALID_ARG, "v_scale is NULL (full-int8)");
   if (p->write_o) {
     if (!p->o) return set_error(INTFA_ERR_INVALID_ARG, "o is NULL");

@@ -129,6 +129,7 @@ struct TileInfo {
   int bh, b, h, hk, mb, work, nsteps;   // hk: the K/V head this query head reads (grouped-query attention)
 };
 
+template <bool RAGGED = false>
 __device__ __forceinline__ TileInfo decode_tile(const KParams& p, int tile, int G) {
   TileInfo t;
   t.bh = tile / p.MB;
@@ -139,6 +140,7 @@ __device__ __forceinline__ TileInfo decode_tile(const KParams& p, int tile, int 
   t.hk = t.h / p.hk_ratio;
   t.work = t.bh * p.MB + t.mb;
   int n = p.Nk / G;
+  if constexpr (RAGGED) n = (p.Nk + G - 1) / G;  // the last KV step may be partial
   if (p.causal) {
     // last visible global column for the last row of the block
     const long long last_row = p.q_off + (long long)t.mb * kBM + (kBM - 1);
@@ -918,7 +920,7 @@ static int launch(const IntfaFwdParams* a, const KParams& kp, cudaStream_t strea
 }
 
 // Pipelined full-int8 kernel: one CTA per SM.
-template <int D, int G, bool FULL, bool PRNE>
+template <int D, int G, bool FULL, bool PRNE, bool RAGGED>
 static int launch_pipe(const IntfaFwdParams* a, const KParams& kp, cudaStream_t stream) {
   using C = PipeCfg<D, G, FULL>;
   static_assert(C::SMEM_BYTES <= 227 * 1024, "shared memory");
@@ -932,7 +934,7 @@ static int launch_pipe(const IntfaFwdParams* a, const KParams& kp, cudaStream_t 
   } else {
     if ((rc = make_tmap(&tmV, a->v, 2, a->v_stride, a->B, kv_heads(a), a->Nk, D, 64, G, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   }
-  auto kern = intfa_fwd_pipe_kernel<D, G, FULL, PRNE>;
+  auto kern = intfa_fwd_pipe_kernel<D, G, FULL, PRNE, RAGGED>;
   static bool attr_done = false;
   static int attr_dev = -1;
   int dev = 0;
@@ -973,7 +975,7 @@ int fwd_dispatch(const IntfaFwdParams* a, cudaStream_t stream) {
   kp.state_in = a->state_in; kp.state_out = a->state_out; kp.write_o = a->write_o;
   kp.dbg_s = a->dbg_s; kp.dbg_p = a->dbg_p; kp.dbg_tile = a->dbg_tile; kp.dbg_step = a->dbg_step;
   kp.status = a->status;
-  kp.MB = a->Nq / kBM;
+  kp.MB = (a->Nq + kBM - 1) / kBM;            // the last query tile may be partial (pipelined kernel only)
   kp.num_tiles = a->B * a->H * kp.MB;
   const bool full = a->variant == INTFA_VARIANT_FULL;
   const bool rne = full && a->p_round == 1;
@@ -981,11 +983,18 @@ int fwd_dispatch(const IntfaFwdParams* a, cudaStream_t stream) {
   // The one-CTA pipelined kernel serves full-int8 and half-int8 at head_dim 128; half-int8 at head_dim 64 is
   // faster on the two-CTA kernel (measured), which INTFA_LEGACY_KERNEL in the environment selects for everything.
   static const bool use_pipe = getenv("INTFA_LEGACY_KERNEL") == nullptr;
+  // Sequence lengths that are not multiples of the tile sizes: only the pipelined kernel masks them
+  const bool ragged = (a->Nq % kBM) != 0 || (a->Nk % a->G) != 0;
+  if (ragged && !use_pipe)
+    return set_error(INTFA_ERR_UNSUPPORTED, "Nq=%d / Nk=%d not multiples of 128 / G=%d: not supported by the kernel INTFA_LEGACY_KERNEL selects", a->Nq, a->Nk, a->G);
 #define INTFA_CASE(DD, GG)                                                       \
   if (D == DD && G == GG) {                                                      \
-    if (full && use_pipe) return rne ? launch_pipe<DD, GG, true, true>(a, kp, stream)  \
-                                     : launch_pipe<DD, GG, true, false>(a, kp, stream);\
-    if (use_pipe && DD == 128) return launch_pipe<DD, GG, false, false>(a, kp, stream); \
+    if (full && use_pipe && ragged) return rne ? launch_pipe<DD, GG, true, true, true>(a, kp, stream)   \
+                                               : launch_pipe<DD, GG, true, false, true>(a, kp, stream); \
+    if (full && use_pipe) return rne ? launch_pipe<DD, GG, true, true, false>(a, kp, stream)            \
+                                     : launch_pipe<DD, GG, true, false, false>(a, kp, stream);          \
+    if (use_pipe && ragged) return launch_pipe<DD, GG, false, false, true>(a, kp, stream);              \
+    if (use_pipe && DD == 128) return launch_pipe<DD, GG, false, false, false>(a, kp, stream);          \
     if (full) return rne ? launch<DD, GG, true, true>(a, kp, stream)             \
                          : launch<DD, GG, true, false>(a, kp, stream);           \
     return launch<DD, GG, false, false>(a, kp, stream);                          \

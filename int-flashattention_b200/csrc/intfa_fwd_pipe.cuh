@@ -73,7 +73,9 @@ struct PipeCfg {
 enum PipeWait { PW_TILE = 32, PW_QE, PW_KE, PW_VE, PW_QF, PW_KF, PW_VF, PW_SFREE, PW_PFULL, PW_OFREE, PW_SFULL,
                 PW_PFREE, PW_OFULL, PW_FIN, PW_FINFREE, PW_HM, PW_HL, PW_AFULL };
 
-template <int D, int G, bool FULL, bool PRNE>
+// RAGGED: Nq / Nk are not multiples of 128 / G -- the last query tile and the last KV step are partial.  A separate
+// instantiation, so that the code of the common case stays as small as it was (instruction cache).
+template <int D, int G, bool FULL, bool PRNE, bool RAGGED>
 __global__ void __launch_bounds__(kPipeThreads, 1)
 intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const KParams p) {
@@ -201,7 +203,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         mbar_arrive(BAR(B_TILE + (tseq & 3u)));
         ++tseq;
         if (tile < 0) break;
-        const TileInfo t = decode_tile(p, tile, G);
+        const TileInfo t = decode_tile<RAGGED>(p, tile, G);
         if (t.nsteps == 0) continue;
         ok = mbar_wait(BAR(B_QEMPTY), (tile_it & 1) ^ 1, abort_flag, p.status, code_hi | PW_QE);
         if (!ok) break;
@@ -269,7 +271,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       while (ok) {
         const int tile = next_tile(tseq, lane == 0, true);
         if (tile < 0) break;
-        const TileInfo t = decode_tile(p, tile, G);
+        const TileInfo t = decode_tile<RAGGED>(p, tile, G);
         if (t.nsteps == 0) continue;
         INTFA_T0();
         ok = mbar_wait_warp(BAR(B_QFULL), tile_it & 1, abort_flag, p.status, code_hi | PW_QF);

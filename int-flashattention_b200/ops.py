@@ -113,6 +113,11 @@ def _fwd(variant, q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, *, G=Non
         G = default_G(D, variant)
     q, k, v = _prep_main(q), _prep_main(k), _prep_main(v)
     qs, ks = _scales_f32(q_scale), _scales_f32(k_scale)
+    if Nk % G:
+        # the kernel fetches the K scales of a KV step G at a time: give every row room up to the next multiple of G
+        ks_pad = torch.zeros(ks.shape[:2] + ((Nk + G - 1) // G * G,), dtype=torch.float32, device=ks.device)
+        ks_pad[:, :, :Nk] = ks
+        ks = ks_pad
     o = torch.empty((B, H, Nq, D) if write_o else (1, 1, 1, 8), dtype=out_dtype, device=q.device)  # :194-195
 
     P = _lib.IntfaFwdParams()

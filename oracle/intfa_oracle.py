@@ -108,10 +108,28 @@ def int8_attention(q8, k8, v, q_scale, k_scale, v_scale, causal, sm_scale, *,
     masked formula when causal.  `state`=(m,l,acc) continues a previous call
     (ring attention); q_offset/kv_offset are the global positions of row 0 / col 0.
     Returns o fp16 [B,H,Nq,d] (and optionally the (m,l,acc) state).
+
+    Sequence lengths that are not multiples of the block sizes (the Triton ops leave them unchecked; the
+    CUDA path masks them, csrc/mask.h:277-285): rows and columns are padded with zeros up to the next
+    multiple, padded COLUMNS get the bias -1e6 of the masked formula (so p = 0 exactly) in the one KV
+    group they fall into, padded rows are dropped from every result.
     """
-    B, H, Nq, d = q8.shape
-    Nk = k8.shape[2]
-    assert Nq % block_m == 0 and Nk % G == 0 and block_m % G == 0
+    B, H, Nq_valid, d = q8.shape
+    Nk_valid = k8.shape[2]
+    assert block_m % G == 0 or G % block_m == 0
+    pad_q = (-Nq_valid) % block_m
+    pad_k = (-Nk_valid) % G
+    if pad_q or pad_k:
+        F = torch.nn.functional
+        q8 = F.pad(q8, (0, 0, 0, pad_q))
+        q_scale = F.pad(q_scale, (0, pad_q))
+        k8 = F.pad(k8, (0, 0, 0, pad_k))
+        k_scale = F.pad(k_scale, (0, pad_k))
+        v = F.pad(v, (0, 0, 0, pad_k))
+        if state is not None:
+            state = (F.pad(state[0], (0, pad_q)), F.pad(state[1], (0, pad_q), value=1.0),
+                     F.pad(state[2], (0, 0, 0, pad_q)))
+    Nq, Nk = Nq_valid + pad_q, Nk_valid + pad_k
     c = torch.tensor(qk_scale_f32(sm_scale))
     qs = q_scale.to(torch.float32)
     ks = k_scale.to(torch.float32)
@@ -133,10 +151,13 @@ def int8_attention(q8, k8, v, q_scale, k_scale, v_scale, causal, sm_scale, *,
         S = _imatmul(q8[:, :, rows], kj.transpose(-1, -2))                 # :36 exact int32
         s = S * qs[:, :, rows, None]                                       # :37
         s = s * ks[:, :, None, n0:n0 + G]                                  # :38
-        if masked:
+        tail = n0 + G > Nk_valid                                          # the group holds padded columns
+        if masked or tail:
             row_id = torch.arange(rows.start, rows.stop)[:, None] + q_offset
             col_id = torch.arange(n0, n0 + G)[None, :] + kv_offset
-            bias = torch.where(row_id >= col_id, torch.tensor(0.0), torch.tensor(-1.0e6))
+            vis = (row_id >= col_id) if masked else torch.ones(1, 1, dtype=torch.bool)
+            vis = vis & (torch.arange(n0, n0 + G)[None, :] < Nk_valid)
+            bias = torch.where(vis, torch.tensor(0.0), torch.tensor(-1.0e6))
             x = s * c + bias                                               # :41
             m_new = torch.maximum(m_r, x.max(-1).values)                   # :42
             x = x - m_new[..., None]                                       # :43
@@ -181,6 +202,8 @@ def int8_attention(q8, k8, v, q_scale, k_scale, v_scale, causal, sm_scale, *,
                     m_r, l_r, acc_r = step(rows, n0, True, m_r, l_r, acc_r)
             m[:, :, rows], l[:, :, rows], acc[:, :, rows] = m_r, l_r, acc_r
 
+    if pad_q:
+        m, l, acc = m[:, :, :Nq_valid], l[:, :, :Nq_valid], acc[:, :, :Nq_valid]
     o = (acc / l[..., None]).to(torch.float16)                             # :181-182
     if return_state:
         return o, (m, l, acc)

@@ -70,7 +70,7 @@ def test_validation_rejects_before_launch(lib):
     assert "head_dim" in lib.last_error()
     P.D = 128
     P.Nq = 100
-    assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_UNSUPPORTED       # ragged Nq
+    assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_INVALID_ARG       # a ragged Nq is fine; q is NULL
     P.Nq = 128
     P.G = 96
     assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_UNSUPPORTED       # G must be 64 or 128
