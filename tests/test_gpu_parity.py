@@ -199,6 +199,30 @@ def test_bench_style_inputs_run(pkg, oracle, dev):
     _close(oracle, out.float() / scale, ref.float() / scale, tight=False)
 
 
+@pytest.mark.parametrize("variant", ["full", "half"])
+def test_acc_test_style_inputs(variant, pkg, oracle, dev):
+    """The reference's own accuracy run (benchmark.py:133-185): U(0,1) fp16 inputs, sm_scale 1, non-causal,
+    per-token Q/K and per-(batch,head) V quantisation -- here at head_dim 64, asserted against the oracle, and with
+    the error against exact attention no worse than the oracle's."""
+    B, H, N, D = 1, 2, 1024, 64
+    g = torch.Generator().manual_seed(20)
+    q, k, v = (torch.rand(B, H, N, D, generator=g).half() for _ in range(3))
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    ex = oracle.exact_attention(q, k, v, False, 1.0)
+    if variant == "full":
+        v8, vs = oracle.quant_pertensor(v)
+        ref = oracle.attention_full_int8(q8, k8, v8, qs, ks, vs, False, 1.0, G=64)
+        out = pkg.attention_full_int8(q8.to(dev), k8.to(dev), v8.to(dev), qs.to(dev), ks.to(dev), vs.to(dev), False, 1.0)
+    else:
+        ref = oracle.attention_int8(q8, k8, v, qs, ks, False, 1.0, G=64)
+        out = pkg.attention_int8(q8.to(dev), k8.to(dev), v.to(dev), qs.to(dev), ks.to(dev), False, 1.0)
+    pkg.check_status()
+    _close(oracle, out, ref)
+    e_out, e_ref = oracle.err_metrics(out.cpu(), ex), oracle.err_metrics(ref, ex)
+    assert e_out["mean_rel"] <= e_ref["mean_rel"] * 1.02 + 1e-6
+
+
 def test_arbitrary_fp32_scales(pkg, oracle, dev):
     """Scales that are NOT fp16-representable take the kernel's general dequantisation path
     (the one-fma shortcut is only exact for fp16-valued scales)."""
