@@ -70,9 +70,10 @@ int intfa_fwd(const IntfaFwdParams* p, void* stream) {
   const bool full = p->variant == INTFA_VARIANT_FULL;
   if (p->B <= 0 || p->H <= 0 || p->Nq <= 0 || p->Nk <= 0)
     return set_error(INTFA_ERR_INVALID_ARG, "B, H, Nq, Nk must be positive");
-  if (p->D != 64 && p->D != 128)
-    return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: the sm_100a kernels cover 64 and 128", p->D);
-  if (p->G != 64 && p->G != 128) return set_error(INTFA_ERR_UNSUPPORTED, "G=%d unsupported: 64 or 128", p->G);
+  if (p->D != 32 && p->D != 64 && p->D != 128)
+    return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: the sm_100a kernels cover 32, 64 and 128", p->D);
+  if (p->G != 64 && p->G != 128 && !(p->G == 32 && p->D == 32 && full))
+    return set_error(INTFA_ERR_UNSUPPORTED, "G=%d unsupported: 64 or 128 (32 for full-int8 at head_dim 32)", p->G);
   if (p->p_round != 0 && p->p_round != 1) return set_error(INTFA_ERR_INVALID_ARG, "p_round must be 0 or 1");
   if (p->H_kv < 0 || (p->H_kv > 0 && p->H % p->H_kv != 0))
     return set_error(INTFA_ERR_INVALID_ARG, "H=%d must be a multiple of H_kv=%d", p->H, p->H_kv);
@@ -114,7 +115,7 @@ static int check_quant_args(const void* x, const int64_t* st, const void* x8, co
                             int D) {
   if (!x || !st || !x8 || !scale) return set_error(INTFA_ERR_INVALID_ARG, "NULL argument");
   if (B <= 0 || H <= 0 || N <= 0) return set_error(INTFA_ERR_INVALID_ARG, "B, H, N must be positive");
-  if (D != 64 && D != 128) return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: 64 or 128", D);
+  if (D != 32 && D != 64 && D != 128) return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: 32, 64 or 128", D);
   if (!aligned16(x) || st[0] % 8 || st[1] % 8 || st[2] % 8)
     return set_error(INTFA_ERR_INVALID_ARG, "input rows must be 16-byte aligned (pointer and strides multiples of 8 elements)");
   if (!aligned16(x8)) return set_error(INTFA_ERR_INVALID_ARG, "int8 output must be 16-byte aligned");
@@ -149,7 +150,7 @@ int intfa_v_colmax(const void* v, const int64_t v_stride[3], void* colmax, int32
                    void* stream) {
   if (!v || !v_stride || !colmax) return set_error(INTFA_ERR_INVALID_ARG, "NULL argument");
   if (B <= 0 || H <= 0 || N <= 0) return set_error(INTFA_ERR_INVALID_ARG, "B, H, N must be positive");
-  if (D != 64 && D != 128) return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: 64 or 128", D);
+  if (D != 32 && D != 64 && D != 128) return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: 32, 64 or 128", D);
   if (!aligned16(v) || v_stride[0] % 8 || v_stride[1] % 8 || v_stride[2] % 8)
     return set_error(INTFA_ERR_INVALID_ARG, "input rows must be 16-byte aligned (pointer and strides multiples of 8 elements)");
   if ((long long)B * H > 65535) return set_error(INTFA_ERR_TOO_LARGE, "B*H=%lld exceeds 65535", (long long)B * H);

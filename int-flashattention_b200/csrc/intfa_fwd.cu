@@ -925,14 +925,16 @@ static int launch_pipe(const IntfaFwdParams* a, const KParams& kp, cudaStream_t 
   using C = PipeCfg<D, G, FULL>;
   static_assert(C::SMEM_BYTES <= 227 * 1024, "shared memory");
   CUtensorMap tmQ, tmK, tmV;
-  const CUtensorMapSwizzle swzD = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  const CUtensorMapSwizzle swzD = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : (D == 64) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
   int rc;
   if ((rc = make_tmap(&tmQ, a->q, 1, a->q_stride, a->B, a->H, a->Nq, D, D, kBM, swzD))) return rc;
   if ((rc = make_tmap(&tmK, a->k, 1, a->k_stride, a->B, kv_heads(a), a->Nk, D, D, G, swzD))) return rc;
   if constexpr (FULL) {
     if ((rc = make_tmap(&tmV, a->v, 1, a->v_stride, a->B, kv_heads(a), a->Nk, D, D, G, swzD))) return rc;
   } else {
-    if ((rc = make_tmap(&tmV, a->v, 2, a->v_stride, a->B, kv_heads(a), a->Nk, D, 64, G, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    if ((rc = make_tmap(&tmV, a->v, 2, a->v_stride, a->B, kv_heads(a), a->Nk, D, D >= 64 ? 64 : D, G,
+                        D >= 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
   }
   auto kern = intfa_fwd_pipe_kernel<D, G, FULL, PRNE, RAGGED>;
   static bool attr_done = false;
@@ -1004,7 +1006,23 @@ int fwd_dispatch(const IntfaFwdParams* a, cudaStream_t stream) {
   INTFA_CASE(64, 64)
   INTFA_CASE(64, 128)
 #undef INTFA_CASE
-  return set_error(INTFA_ERR_UNSUPPORTED, "unsupported (D=%d, G=%d): supported are (128,128), (128,64), (64,64), (64,128)", D, G);
+  // head_dim 32: the pipelined kernel only (G = 32 for full-int8 only: fp16 P tiles need 64 columns)
+#define INTFA_CASE32(GG)                                                                                          \
+  if (D == 32 && G == GG && use_pipe) {                                                                           \
+    if (full && ragged) return rne ? launch_pipe<32, GG, true, true, true>(a, kp, stream)                         \
+                                   : launch_pipe<32, GG, true, false, true>(a, kp, stream);                       \
+    if (full) return rne ? launch_pipe<32, GG, true, true, false>(a, kp, stream)                                  \
+                         : launch_pipe<32, GG, true, false, false>(a, kp, stream);                                \
+    if constexpr (GG >= 64) {                                                                                     \
+      return ragged ? launch_pipe<32, GG, false, false, true>(a, kp, stream)                                      \
+                    : launch_pipe<32, GG, false, false, false>(a, kp, stream);                                    \
+    }                                                                                                             \
+  }
+  INTFA_CASE32(32)
+  INTFA_CASE32(64)
+  INTFA_CASE32(128)
+#undef INTFA_CASE32
+  return set_error(INTFA_ERR_UNSUPPORTED, "unsupported (D=%d, G=%d, %s): supported are D in {64,128} with G in {64,128}, and D=32 with G in {32,64,128} (G=32: full-int8 only; not with INTFA_LEGACY_KERNEL)", D, G, full ? "full-int8" : "half-int8");
 }
 
 }  // namespace intfa

@@ -57,12 +57,16 @@ struct PipeCfg {
   static constexpr int SMEM_BYTES = OFF_MISC + 32 + 1024;
   static constexpr int COL_S = 0, COL_O = 2 * G, COL_ACC = FULL ? 2 * G + D : 2 * G;   // S buffer b at COL_S + b*G; no O_j for half-int8
   static constexpr int TMEM_COLS = 512;
-  static constexpr uint64_t SWZ_QK = (D == 128) ? kSwz128 : kSwz64;
+  static_assert(FULL || G >= 64, "half-int8: fp16 P tiles are built from 64-column blocks");
+  static constexpr uint64_t SWZ_QK = (D == 128) ? kSwz128 : (D == 64) ? kSwz64 : kSwz32;       // Q, K rows are D bytes
   static constexpr uint32_t SBO_QK = 8 * D;
-  static constexpr uint64_t SWZ_P = FULL ? ((G == 128) ? kSwz128 : kSwz64) : kSwz128;
+  static constexpr uint64_t SWZ_P = FULL ? ((G == 128) ? kSwz128 : (G == 64) ? kSwz64 : kSwz32) : kSwz128;
   static constexpr uint32_t SBO_P = FULL ? 8 * G : 1024;
-  static constexpr uint64_t SWZ_V = FULL ? ((D == 128) ? kSwz128 : kSwz64) : kSwz128;
-  static constexpr uint32_t SBO_V = FULL ? 8 * D : 1024;
+  // V rows: D bytes (int8), or boxes of min(D, 64) fp16 channels = 128 / 64 bytes
+  static constexpr int V_BOXES = FULL ? 1 : (D >= 64 ? D / 64 : 1);
+  static constexpr int V_ROWB = FULL ? D : (D >= 64 ? 128 : 2 * D);
+  static constexpr uint64_t SWZ_V = (V_ROWB == 128) ? kSwz128 : (V_ROWB == 64) ? kSwz64 : kSwz32;
+  static constexpr uint32_t SBO_V = 8 * V_ROWB;
   static constexpr uint32_t IDESC_QK = make_idesc(2, 1, 1, 0, 0, kBM, G);
   static constexpr uint32_t IDESC_PV = FULL ? make_idesc(2, 1, 1, 0, 1, kBM, D) : make_idesc(1, 0, 0, 0, 1, kBM, D);
   // fp16 x fp16 -> fp32, K = 16: writes the fp32 constant 1.5*2^23 into a whole accumulator tile
@@ -224,7 +228,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tma_load_4d(sV + s * C::V_BYTES, &tmV, BAR(B_VFULL + s), 0, j * G, t.hk, t.b);
           } else {
 #pragma unroll
-            for (int c = 0; c < D / 64; ++c)
+            for (int c = 0; c < C::V_BOXES; ++c)
               tma_load_4d(sV + s * C::V_BYTES + c * (G * 128), &tmV, BAR(B_VFULL + s), c * 64, j * G, t.hk, t.b);
           }
         }
@@ -317,7 +321,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
               const uint32_t keep = (j > 0 || p.state_in) ? 1u : 0u;
 #pragma unroll
               for (int kk = 0; kk < G / 16; ++kk)
-                umma_f16(tA, ad0 + (uint64_t)((kk >> 2) * ((kBM * 128) >> 4) + (kk & 3) * 2), vd0 + (uint64_t)(kk * (2048 >> 4)),
+                umma_f16(tA, ad0 + (uint64_t)((kk >> 2) * ((kBM * 128) >> 4) + (kk & 3) * 2), vd0 + (uint64_t)(kk * ((16 * C::V_ROWB) >> 4)),
                          C::IDESC_PV, kk > 0 ? 1u : keep);
             }
             umma_commit(BAR(B_OFULL));

@@ -155,7 +155,7 @@ __device__ __forceinline__ void tc_fence_after() {
 //   SBO = bytes between 8-row groups, LBO unused (1).
 // MN-major operand (rows of the tile are K indices, contiguous along M/N):
 //   SBO = bytes between 8-row (K) groups, LBO = bytes between swizzle-span-wide MN chunks.
-constexpr uint64_t kSwz128 = 2, kSwz64 = 4;
+constexpr uint64_t kSwz128 = 2, kSwz64 = 4, kSwz32 = 6;
 
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
                                                    uint64_t swizzle) {

@@ -256,8 +256,10 @@ int quant_pertoken(const void* x, const int64_t* st, void* x8, float* scale, int
   quant_pertoken_kernel<DD, CC><<<grid, 256, 0, stream>>>((const __half*)x, st[0], st[1], st[2], (int8_t*)x8, scale, H, N, rows)
   if (D == 128) {
     if (contig) INTFA_QPT(128, true); else INTFA_QPT(128, false);
-  } else {
+  } else if (D == 64) {
     if (contig) INTFA_QPT(64, true); else INTFA_QPT(64, false);
+  } else {
+    if (contig) INTFA_QPT(32, true); else INTFA_QPT(32, false);
   }
 #undef INTFA_QPT
   return check_launch("quant_pertoken");
@@ -280,8 +282,10 @@ int v_colmax(const void* v, const int64_t* st, void* colmax, int B, int H, int N
   dim3 grid(v_grid(B * H, N, sms, &rows_per_cta), B * H);
   if (D == 128)
     v_colmax_kernel<128><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (unsigned int*)colmax, H, N, rows_per_cta);
-  else
+  else if (D == 64)
     v_colmax_kernel<64><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (unsigned int*)colmax, H, N, rows_per_cta);
+  else
+    v_colmax_kernel<32><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (unsigned int*)colmax, H, N, rows_per_cta);
   return check_launch("v_colmax");
 }
 
@@ -294,8 +298,10 @@ int v_quant_from_colmax(const void* v, const int64_t* st, const void* colmax, vo
   const int pc = mode == INTFA_VSCALE_PER_CHANNEL;
   if (D == 128)
     v_quant_kernel<128><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (const unsigned int*)colmax, (int8_t*)v8, scale, pc, H, N, rows_per_cta);
-  else
+  else if (D == 64)
     v_quant_kernel<64><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (const unsigned int*)colmax, (int8_t*)v8, scale, pc, H, N, rows_per_cta);
+  else
+    v_quant_kernel<32><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (const unsigned int*)colmax, (int8_t*)v8, scale, pc, H, N, rows_per_cta);
   return check_launch("v_quant");
 }
 

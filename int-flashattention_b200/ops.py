@@ -28,7 +28,7 @@ def default_G(head_dim, variant="full"):
     rounding, and 128-wide KV tiles are the faster ones at both head sizes."""
     if variant == "half":
         return 128
-    return 128 if head_dim >= 128 else 64
+    return 128 if head_dim >= 128 else (64 if head_dim >= 64 else 32)
 
 
 def _stream(t):

@@ -65,8 +65,8 @@ def test_version_and_error_text(lib):
 def test_validation_rejects_before_launch(lib):
     h = lib.load()
     P = lib.IntfaFwdParams()
-    P.B, P.H, P.Nq, P.Nk, P.D, P.G = 1, 1, 128, 128, 32, 64
-    assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_UNSUPPORTED       # head_dim 32
+    P.B, P.H, P.Nq, P.Nk, P.D, P.G = 1, 1, 128, 128, 16, 64
+    assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_UNSUPPORTED       # head_dim 16
     assert "head_dim" in lib.last_error()
     P.D = 128
     P.Nq = 100
