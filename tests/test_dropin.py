@@ -1,0 +1,44 @@
+"""The drop-in modules, driven the way the reference's benchmark.py drives its own: `from flash_atten_int8 import
+attention_int8`, `from flash_atten_full_int8 import attention_full_int8` (benchmark.py:12-13), positional arguments,
+scales as quant_pertoken / quant_pertensor make them (fp16), at the shapes of its acc_test call (benchmark.py:212:
+N_CTX=32, HEAD_DIM=32) and of its bench sweep (HEAD_DIM=64, benchmark.py:23)."""
+import importlib
+import os
+import sys
+
+import pytest
+import torch
+
+DROPIN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "int-flashattention_b200", "dropin")
+
+
+def _modules():
+    if DROPIN not in sys.path:
+        sys.path.insert(0, DROPIN)
+    return importlib.import_module("flash_atten_int8"), importlib.import_module("flash_atten_full_int8")
+
+
+def test_dropin_modules_export_the_reference_names():
+    half, full = _modules()
+    assert callable(half.attention_int8) and callable(full.attention_full_int8)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,H,N,D", [(1, 2, 32, 32), (2, 4, 1024, 64)])
+def test_acc_test_call_pattern(B, H, N, D, oracle):
+    half, full = _modules()
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(20)
+    q, k, v = (torch.rand(B, H, N, D, generator=g).half() for _ in range(3))     # benchmark.py:140-142
+    q8, qs = oracle.quant_pertoken(q)                                              # :158-160
+    k8, ks = oracle.quant_pertoken(k)
+    v8, vs = oracle.quant_pertensor(v)
+    G = 32 if D == 32 else 64
+    o_half = half.attention_int8(q8.to(dev), k8.to(dev), v.to(dev), qs.to(dev), ks.to(dev), False, 1.0)
+    o_full = full.attention_full_int8(q8.to(dev), k8.to(dev), v8.to(dev), qs.to(dev), ks.to(dev), vs.to(dev), False, 1.0)
+    r_half = oracle.attention_int8(q8, k8, v, qs, ks, False, 1.0, G=G)
+    r_full = oracle.attention_full_int8(q8, k8, v8, qs, ks, vs, False, 1.0, G=G)
+    for o, r in ((o_half, r_half), (o_full, r_full)):
+        assert o.dtype == torch.float16 and o.shape == (B, H, N, D)
+        e = oracle.err_metrics(o.cpu(), r)
+        assert e["max_abs"] <= 4e-3 and e["mean_rel"] <= 3e-4, e
