@@ -54,7 +54,9 @@ def test_quant_pertoken_strided_input(pkg, oracle, dev):
     assert torch.equal(g8.cpu(), r8) and torch.equal(gs.cpu(), rs.float())
 
 
-@pytest.mark.parametrize("B,H,N,D", [(1, 4, 512, 64), (2, 3, 384, 128), (1, 1, 4096, 128)])
+# (the last three shapes: many (batch, head) slabs; one of them with a ragged length, one at head_dim 32)
+@pytest.mark.parametrize("B,H,N,D", [(1, 4, 512, 64), (2, 3, 384, 128), (1, 1, 4096, 128), (4, 8, 1024, 128),
+                                     (2, 16, 333, 64), (8, 8, 40, 32)])
 def test_quant_v_bit_exact(B, H, N, D, pkg, oracle, dev):
     _, _, v = make_qkv(23, B, H, N, D)
     v[..., 5] = 0                                    # an all-zero channel
