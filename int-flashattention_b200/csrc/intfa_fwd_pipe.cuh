@@ -21,13 +21,13 @@
 // Arithmetic is the same as in intfa_fwd_kernel (see the contract at the top of intfa_fwd.cu).
 #pragma once
 
-constexpr int kPipeThreads = 640;
+constexpr int kPipeThreads = 512;
 constexpr int kPipeSoftmaxThreads = 256;
-constexpr int kPipeCorrThreads = 256;
+constexpr int kPipeCorrThreads = 128;
 // Registers: the CTA is launched with kPipeLaunchRegs per thread and setmaxnreg only moves registers around
 // INSIDE that allocation -- an increase beyond it would block for ever, hence the static_assert.
 constexpr int kPipeLaunchRegs = (65536 / kPipeThreads) / 8 * 8;
-constexpr int kPipeServiceRegs = 40, kPipeSoftmaxRegs = 128, kPipeCorrRegs = 80;
+constexpr int kPipeServiceRegs = 40, kPipeSoftmaxRegs = 184, kPipeCorrRegs = 104;
 static_assert(128 * kPipeServiceRegs + kPipeSoftmaxThreads * kPipeSoftmaxRegs + kPipeCorrThreads * kPipeCorrRegs <=
                   kPipeThreads * kPipeLaunchRegs, "setmaxnreg budget exceeds the registers the CTA is launched with");
 
@@ -52,7 +52,7 @@ struct PipeCfg {
   static constexpr int OFF_MAGIC = OFF_FIN + 2 * 128 * 8;          // 4 KB constant fp16 operand of the "arm" MMA
   static constexpr int MAGIC_BYTES = 4096;
   static constexpr int OFF_BAR = OFF_MAGIC + MAGIC_BYTES;
-  static constexpr int NUM_BARS = 18 + 4 * NS + 8 + 4;
+  static constexpr int NUM_BARS = 18 + 4 * NS + 8 + 4 + 2;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 32 + 1024;
   static constexpr int COL_S = 0, COL_O = 2 * G, COL_ACC = FULL ? 2 * G + D : 2 * G;   // S buffer b at COL_S + b*G; no O_j for half-int8
@@ -75,7 +75,7 @@ struct PipeCfg {
 };
 
 enum PipeWait { PW_TILE = 32, PW_QE, PW_KE, PW_VE, PW_QF, PW_KF, PW_VF, PW_SFREE, PW_PFULL, PW_OFREE, PW_SFULL,
-                PW_PFREE, PW_OFULL, PW_FIN, PW_FINFREE, PW_HM, PW_HL, PW_AFULL };
+                PW_PFREE, PW_HM, PW_OFULL, PW_FIN, PW_FINFREE, PW_HL, PW_AFULL };
 
 // RAGGED: Nq / Nk are not multiples of 128 / G -- the last query tile and the last KV step are partial.  A separate
 // instantiation, so that the code of the common case stays as small as it was (instruction cache).
@@ -109,6 +109,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   constexpr int B_KFULL = 18, B_KEMPTY = 18 + NS, B_VFULL = 18 + 2 * NS, B_VEMPTY = 18 + 3 * NS;
   constexpr int B_TILE = 18 + 4 * NS, B_TDONE = B_TILE + 4;
   constexpr int B_AFULL = B_TDONE + 4;   // [4] half-int8: alpha of step j (slot j mod 4) published, for the accumulator warps
+  constexpr int B_SFREE = B_AFULL + 4;   // [2] softmax group b (4 warps): S buffer b is in its registers
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 4);
   volatile int* tile_slot = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 16);
@@ -120,13 +121,14 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       mbar_init(BAR(B_SFULL + b), 1);
       mbar_init(BAR(B_PFULL + b), 4);
       mbar_init(BAR(B_PFREE + b), 1);
-      mbar_init(BAR(B_FINFREE + b), 8);
+      mbar_init(BAR(B_FINFREE + b), 4);
+      mbar_init(BAR(B_SFREE + b), 4);
       mbar_init(BAR(B_HM + b), 4);
       mbar_init(BAR(B_HL + b), 4);
       mbar_init(BAR(B_FIN + b), 4);
     }
     mbar_init(BAR(B_OFULL), 1);
-    mbar_init(BAR(B_OFREE), 8);
+    mbar_init(BAR(B_OFREE), 4);
     for (int s = 0; s < NS; ++s) {
       mbar_init(BAR(B_KFULL + s), 1);
       mbar_init(BAR(B_KEMPTY + s), 1);
@@ -135,7 +137,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(BAR(B_TILE + i), 1);
-      mbar_init(BAR(B_TDONE + i), 17);       // MMA warp + 8 softmax warps + 8 updater warps
+      mbar_init(BAR(B_TDONE + i), 14);       // 2 MMA warps + 8 softmax warps + 4 accumulator warps
       mbar_init(BAR(B_AFULL + i), 4);
     }
     *abort_flag = 0;
@@ -238,27 +240,24 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     __syncwarp();
   } else if (warp == 1) {
     {
-      // ------------------------------------------------------------------ MMA issuer
+      // ------------------------------------------------------------------ MMA issuer for S = Q K^T
       // The whole warp runs the loop and the waits (warp-uniform control flow keeps the descriptor arithmetic
       // off the per-thread path); one elected lane issues the tensor-core instructions.
-      // Order per work item: QK(0), QK(1); then for each step j: [P(j) ready = S buffer of j free] QK(j+2), PV(j).
+      // Order per work item: QK(0), QK(1); then for each step j: [S(j) read out and K scales applied] QK(j+2).
       uint32_t kv_it = 0, tile_it = 0, tseq = 0;
       bool ok = true;
-#ifdef INTFA_TIMING
-      long long tm[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tq;
-#endif
+      INTFA_TDECL();
       // operand descriptors of stage 0 / K step 0; the start-address field (16-byte units) takes the offsets
       const uint64_t descQ0 = make_smem_desc(sQ, 16, C::SBO_QK, C::SWZ_QK);
       const uint64_t descK0 = make_smem_desc(sK, 16, C::SBO_QK, C::SWZ_QK);
-      const uint64_t descP0 = make_smem_desc(sP, 16, C::SBO_P, C::SWZ_P);
-      const uint64_t descV0 = make_smem_desc(sV, FULL ? 16 : G * 128, C::SBO_V, C::SWZ_V);
-      // S buffer (it & 1) must be free: the caller has seen P_FULL of step it-2
+      // S buffer (it & 1) must be free: the caller has seen S_FREE of step it-2
       auto issue_qk = [&](uint32_t it, bool last) -> bool {
         const uint32_t s = it % NS, ph = (it / NS) & 1;
         INTFA_T0();
         if (!mbar_wait_warp(BAR(B_KFULL + s), ph, abort_flag, p.status, code_hi | PW_KF)) return false;
         tc_fence_after();
         INTFA_T(1);
+        INTFA_TR(2, it - 2, 6);
         const uint64_t bd0 = descK0 + (uint64_t)(s * (C::K_BYTES >> 4));
         const uint32_t tSb = tS + (it & 1) * G;
         if (elect_one()) {
@@ -285,29 +284,63 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (ok && t.nsteps > 1) ok = issue_qk(kv_it + 1, t.nsteps == 2);
         if (!ok) break;
         for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
-          const uint32_t s = kv_it % NS, ph = (kv_it / NS) & 1;
+          const uint32_t s = kv_it % NS;
           const uint32_t b = kv_it & 1;
+          // S buffer b is in the registers of its softmax group and the K scales of step j have been applied: the
+          // K stage goes back to the producer and the Q K^T two steps ahead goes into the S buffer now, long before
+          // the group needs it.  (Waited for at every step, so that the phases of the barrier stay in step.)
           INTFA_T0();
-          ok = mbar_wait_warp(BAR(B_PFULL + b), (kv_it >> 1) & 1, abort_flag, p.status, code_hi | PW_PFULL);
+          ok = mbar_wait_warp(BAR(B_SFREE + b), (kv_it >> 1) & 1, abort_flag, p.status, code_hi | PW_SFREE);
           if (!ok) break;
-          INTFA_T(3);
-          // S buffer b is free again: the Q K^T two steps ahead goes first, the softmax group waits for it
-          if (elect_one()) umma_commit(BAR(B_KEMPTY + s));   // K scales of step j have been read as well
+          tc_fence_after();
+          INTFA_T(7);
+          INTFA_TR(2, kv_it, 0);
+          if (elect_one()) umma_commit(BAR(B_KEMPTY + s));
           __syncwarp();
           if (j + 2 < t.nsteps) {
             ok = issue_qk(kv_it + 2, j + 3 == t.nsteps);
             if (!ok) break;
           }
+          INTFA_TR(2, kv_it, 1);
+        }
+        ++tile_it;
+      }
+      INTFA_TDUMP_MMA();
+    }
+    __syncwarp();
+  } else if (warp == 3) {
+    {
+      // ------------------------------------------------------------------ MMA issuer for O_j = P V
+      // A warp of its own, so that a Q K^T whose S buffer is free never queues behind the wait for a P tile.
+      // Per step j: [P(j) written] [V(j) landed] [O_j of step j-1 read out] PV(j).
+      uint32_t kv_it = 0, tseq = 0;
+      bool ok = true;
+      INTFA_TDECL();
+      const uint64_t descP0 = make_smem_desc(sP, 16, C::SBO_P, C::SWZ_P);
+      const uint64_t descV0 = make_smem_desc(sV, FULL ? 16 : G * 128, C::SBO_V, C::SWZ_V);
+      while (ok) {
+        const int tile = next_tile(tseq, lane == 0, true);
+        if (tile < 0) break;
+        const TileInfo t = decode_tile<RAGGED>(p, tile, G);
+        for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
+          const uint32_t s = kv_it % NS, ph = (kv_it / NS) & 1;
+          const uint32_t b = kv_it & 1;
+          // P(j) written; V(j) landed; full-int8: O_j of the previous step has been read out, half-int8: the
+          // accumulator has been brought to this step's running max (and the previous P V has landed in it).
+          // (One copy of the wait code for the three.)
           INTFA_T0();
-          ok = mbar_wait_warp(BAR(B_VFULL + s), ph, abort_flag, p.status, code_hi | PW_VF);
-          if (!ok) break;
-          INTFA_T(4);
-          // full-int8: O_j of the previous step has been read out; half-int8: the accumulator has been brought to
-          // this step's running max (and the previous P V has landed in it)
-          ok = mbar_wait_warp(BAR(B_OFREE), FULL ? ((kv_it & 1) ^ 1) : (kv_it & 1), abort_flag, p.status, code_hi | PW_OFREE);
+#pragma unroll 1
+          for (int w = 0; w < 3; ++w) {
+            const uint32_t wb = w == 0 ? BAR(B_PFULL + b) : w == 1 ? BAR(B_VFULL + s) : BAR(B_OFREE);
+            const uint32_t wp = w == 0 ? ((kv_it >> 1) & 1) : w == 1 ? ph : (FULL ? ((kv_it & 1) ^ 1) : (kv_it & 1));
+            ok = mbar_wait_warp(wb, wp, abort_flag, p.status, code_hi | (w == 0 ? PW_PFULL : w == 1 ? PW_VF : PW_OFREE));
+            if (!ok) break;
+            if (w == 0) { INTFA_TR(2, kv_it, 2); }
+          }
           if (!ok) break;
           tc_fence_after();
           INTFA_T(5);
+          INTFA_TR(2, kv_it, 4);
           const uint64_t ad0 = descP0 + (uint64_t)(b * (C::P_BYTES >> 4));
           const uint64_t vd0 = descV0 + (uint64_t)(s * (C::V_BYTES >> 4));
           if (elect_one()) {
@@ -330,16 +363,22 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           }
           __syncwarp();
           INTFA_T(6);
+          INTFA_TR(2, kv_it, 5);
         }
-        ++tile_it;
       }
-#ifdef INTFA_TIMING
-      if (lane == 0 && p.dbg_s != nullptr && p.dbg_tile == -2 && blockIdx.x < 400) {
-        for (int i = 0; i < 8; ++i) p.dbg_s[12800 + blockIdx.x * 8 + i] = (int)(tm[i] >> 4);
-      }
-#endif
+      INTFA_TDUMP_MMA();
     }
     __syncwarp();
+#ifdef INTFA_TRACE
+  } else if (warp == 2) {
+    // trace builds: timestamps of the completion of S = Q K^T of every step (role 4)
+    if (p.dbg_s != nullptr && p.dbg_tile == -3 && blockIdx.x == 0) {
+      for (uint32_t it = 0; it < (uint32_t)(p.dbg_step + 16); ++it) {
+        if (!mbar_wait_warp(BAR(B_SFULL + (it & 1)), (it >> 1) & 1, abort_flag, p.status, code_hi | PW_SFULL)) break;
+        INTFA_TR(4, it, 0);
+      }
+    }
+#endif
   } else if (warp >= 4 && warp < 12) {
     reg_alloc<kPipeSoftmaxRegs>();
 #include "intfa_fwd_pipe_softmax.inc"
