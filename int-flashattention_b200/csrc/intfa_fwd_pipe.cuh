@@ -27,7 +27,7 @@ constexpr int kPipeCorrThreads = 128;
 // Registers: the CTA is launched with kPipeLaunchRegs per thread and setmaxnreg only moves registers around
 // INSIDE that allocation -- an increase beyond it would block for ever, hence the static_assert.
 constexpr int kPipeLaunchRegs = (65536 / kPipeThreads) / 8 * 8;
-constexpr int kPipeServiceRegs = 40, kPipeSoftmaxRegs = 184, kPipeCorrRegs = 104;
+constexpr int kPipeServiceRegs = 40, kPipeSoftmaxRegs = 136, kPipeCorrRegs = 184;
 static_assert(128 * kPipeServiceRegs + kPipeSoftmaxThreads * kPipeSoftmaxRegs + kPipeCorrThreads * kPipeCorrRegs <=
                   kPipeThreads * kPipeLaunchRegs, "setmaxnreg budget exceeds the registers the CTA is launched with");
 
@@ -38,13 +38,17 @@ struct PipeCfg {
   static constexpr int V_BYTES = FULL ? G * D : G * D * 2;         // int8, or fp16 as D/64 boxes of [G keys][64 channels]
   static constexpr int P_BYTES = FULL ? kBM * G : kBM * G * 2;     // int8, or fp16 as G/64 blocks of [128 rows][64 columns]
   static constexpr int KS_BYTES = G * 4;
-  static constexpr int NS = (FULL || G == 64) ? 4 : 2;
+  static constexpr int NSK = 4;                                    // K stages
+  static constexpr int NSV = (FULL || G == 64) ? 4 : 2;            // V stages (fp16 V tiles are twice the size)
+  static constexpr int NKS = 8;                                    // K-scale slots: a slot is rewritten 8 steps later, when
+                                                                   // the three S buffers have long forced its step out
+  static constexpr int NSB = 3;                                    // S buffers in TMEM
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
-  static constexpr int OFF_V = OFF_K + NS * K_BYTES;
-  static constexpr int OFF_P = OFF_V + NS * V_BYTES;              // two P buffers
+  static constexpr int OFF_V = OFF_K + NSK * K_BYTES;
+  static constexpr int OFF_P = OFF_V + NSV * V_BYTES;             // two P buffers
   static constexpr int OFF_KS = OFF_P + 2 * P_BYTES;
-  static constexpr int OFF_VSD = OFF_KS + NS * KS_BYTES;          // s_v/127 per channel
+  static constexpr int OFF_VSD = OFF_KS + NKS * KS_BYTES;         // s_v/127 per channel
   static constexpr int OFF_HM = OFF_VSD + D * 4;                  // [2 groups][128] float: running max after the group's latest step
   static constexpr int OFF_HL = OFF_HM + 2 * 128 * 4;             // [2 groups][128] float: row sum after the group's latest step
   static constexpr int OFF_ALPHA = OFF_HL + 2 * 128 * 4;          // [4][128] float: alpha of step j for the updater
@@ -52,10 +56,13 @@ struct PipeCfg {
   static constexpr int OFF_MAGIC = OFF_FIN + 2 * 128 * 8;          // 4 KB constant fp16 operand of the "arm" MMA
   static constexpr int MAGIC_BYTES = 4096;
   static constexpr int OFF_BAR = OFF_MAGIC + MAGIC_BYTES;
-  static constexpr int NUM_BARS = 18 + 4 * NS + 8 + 4 + 2;
+  static constexpr int NUM_BARS = 18 + 2 * NSK + 2 * NSV + 8 + 4 + 2 * NSB;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 32 + 1024;
-  static constexpr int COL_S = 0, COL_O = 2 * G, COL_ACC = FULL ? 2 * G + D : 2 * G;   // S buffer b at COL_S + b*G; no O_j for half-int8
+  // S buffer b at COL_S + b*G; then O_j (full-int8: the accumulator itself lives in registers) or the fp32
+  // accumulator the second MMA adds into (half-int8)
+  static constexpr int COL_S = 0, COL_O = NSB * G, COL_ACC = NSB * G;
+  static_assert(NSB * G + D <= 512, "TMEM columns");
   static constexpr int TMEM_COLS = 512;
   static_assert(FULL || G >= 64, "half-int8: fp16 P tiles are built from 64-column blocks");
   static constexpr uint64_t SWZ_QK = (D == 128) ? kSwz128 : (D == 64) ? kSwz64 : kSwz32;       // Q, K rows are D bytes
@@ -84,7 +91,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1)
 intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const KParams p) {
   using C = PipeCfg<D, G, FULL>;
-  constexpr int NS = C::NS;
+  constexpr int NSK = C::NSK, NSV = C::NSV, NSB = C::NSB;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5;
@@ -95,7 +102,6 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   // mbarriers.  "commit" = arrived on by tcgen05.commit, i.e. when the MMAs issued so far are done.
   constexpr int B_QFULL = 0;      // TMA: Q tile landed
   constexpr int B_QEMPTY = 1;     // commit: last Q K^T of the work item done
-  constexpr int B_SFULL = 2;      // [2] commit: S = Q K^T in TMEM buffer b
   constexpr int B_PFULL = 4;      // [2] softmax group b (4 warps): P in shared-memory buffer b, and S buffer b read out
   constexpr int B_PFREE = 6;      // [2] commit: the P V that read P buffer b is done
   constexpr int B_OFULL = 8;      // commit: O_j = P V in TMEM
@@ -106,10 +112,11 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   constexpr int B_FINFREE = 12;   // [2] updater (8 warps): it has read them
   constexpr int B_HM = 14;        // [2] softmax group g (4 warps): running max after its step published
   constexpr int B_HL = 16;        // [2] softmax group g (4 warps): row sum after its step published
-  constexpr int B_KFULL = 18, B_KEMPTY = 18 + NS, B_VFULL = 18 + 2 * NS, B_VEMPTY = 18 + 3 * NS;
-  constexpr int B_TILE = 18 + 4 * NS, B_TDONE = B_TILE + 4;
+  constexpr int B_KFULL = 18, B_KEMPTY = 18 + NSK, B_VFULL = 18 + 2 * NSK, B_VEMPTY = 18 + 2 * NSK + NSV;
+  constexpr int B_TILE = 18 + 2 * NSK + 2 * NSV, B_TDONE = B_TILE + 4;
   constexpr int B_AFULL = B_TDONE + 4;   // [4] half-int8: alpha of step j (slot j mod 4) published, for the accumulator warps
-  constexpr int B_SFREE = B_AFULL + 4;   // [2] softmax group b (4 warps): S buffer b is in its registers
+  constexpr int B_SFULL = B_AFULL + 4;   // [3] commit: S = Q K^T in TMEM buffer b
+  constexpr int B_SFREE = B_SFULL + NSB; // [3] softmax group of the step (4 warps): S buffer b read out for good
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 4);
   volatile int* tile_slot = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 16);
@@ -118,22 +125,26 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     mbar_init(BAR(B_QFULL), 1);
     mbar_init(BAR(B_QEMPTY), 1);
     for (int b = 0; b < 2; ++b) {
-      mbar_init(BAR(B_SFULL + b), 1);
       mbar_init(BAR(B_PFULL + b), 4);
       mbar_init(BAR(B_PFREE + b), 1);
       mbar_init(BAR(B_FINFREE + b), 4);
-      mbar_init(BAR(B_SFREE + b), 4);
       mbar_init(BAR(B_HM + b), 4);
       mbar_init(BAR(B_HL + b), 4);
       mbar_init(BAR(B_FIN + b), 4);
     }
     mbar_init(BAR(B_OFULL), 1);
     mbar_init(BAR(B_OFREE), 4);
-    for (int s = 0; s < NS; ++s) {
+    for (int s = 0; s < NSK; ++s) {
       mbar_init(BAR(B_KFULL + s), 1);
       mbar_init(BAR(B_KEMPTY + s), 1);
+    }
+    for (int s = 0; s < NSV; ++s) {
       mbar_init(BAR(B_VFULL + s), 1);
       mbar_init(BAR(B_VEMPTY + s), 1);
+    }
+    for (int b = 0; b < NSB; ++b) {
+      mbar_init(BAR(B_SFULL + b), 1);
+      mbar_init(BAR(B_SFREE + b), 4);
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(BAR(B_TILE + i), 1);
@@ -217,22 +228,25 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         tma_load_4d(sQ, &tmQ, BAR(B_QFULL), 0, t.mb * kBM, t.h, t.b);
         const float* ks_row = p.ks + (long long)t.b * p.ks_sb + (long long)t.hk * p.ks_sh;
         for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
-          const uint32_t s = kv_it % NS, ph = (kv_it / NS) & 1;
+          const uint32_t s = kv_it % NSK, ph = (kv_it / NSK) & 1;
           ok = mbar_wait(BAR(B_KEMPTY + s), ph ^ 1, abort_flag, p.status, code_hi | PW_KE);
           if (!ok) break;
           mbar_expect_tx(BAR(B_KFULL + s), C::K_BYTES + C::KS_BYTES);
           tma_load_4d(sK + s * C::K_BYTES, &tmK, BAR(B_KFULL + s), 0, j * G, t.hk, t.b);
-          bulk_load_1d(sKS + s * C::KS_BYTES, ks_row + j * G, C::KS_BYTES, BAR(B_KFULL + s));
-          ok = mbar_wait(BAR(B_VEMPTY + s), ph ^ 1, abort_flag, p.status, code_hi | PW_VE);
+          bulk_load_1d(sKS + (kv_it % C::NKS) * C::KS_BYTES, ks_row + j * G, C::KS_BYTES, BAR(B_KFULL + s));
+          INTFA_TR(5, kv_it, 0);
+          const uint32_t sv = kv_it % NSV, phv = (kv_it / NSV) & 1;
+          ok = mbar_wait(BAR(B_VEMPTY + sv), phv ^ 1, abort_flag, p.status, code_hi | PW_VE);
           if (!ok) break;
-          mbar_expect_tx(BAR(B_VFULL + s), C::V_BYTES);
+          mbar_expect_tx(BAR(B_VFULL + sv), C::V_BYTES);
           if constexpr (FULL) {
-            tma_load_4d(sV + s * C::V_BYTES, &tmV, BAR(B_VFULL + s), 0, j * G, t.hk, t.b);
+            tma_load_4d(sV + sv * C::V_BYTES, &tmV, BAR(B_VFULL + sv), 0, j * G, t.hk, t.b);
           } else {
 #pragma unroll
             for (int c = 0; c < C::V_BOXES; ++c)
-              tma_load_4d(sV + s * C::V_BYTES + c * (G * 128), &tmV, BAR(B_VFULL + s), c * 64, j * G, t.hk, t.b);
+              tma_load_4d(sV + sv * C::V_BYTES + c * (G * 128), &tmV, BAR(B_VFULL + sv), c * 64, j * G, t.hk, t.b);
           }
+          INTFA_TR(5, kv_it, 1);
         }
         ++tile_it;
       }
@@ -243,34 +257,15 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       // ------------------------------------------------------------------ MMA issuer for S = Q K^T
       // The whole warp runs the loop and the waits (warp-uniform control flow keeps the descriptor arithmetic
       // off the per-thread path); one elected lane issues the tensor-core instructions.
-      // Order per work item: QK(0), QK(1); then for each step j: [S(j) read out and K scales applied] QK(j+2).
-      uint32_t kv_it = 0, tile_it = 0, tseq = 0;
+      // Step it goes into S buffer it mod 3 as soon as the step three back has been read out of it and K has landed --
+      // up to three steps ahead of the softmax groups.  The K stage is handed back by the tensor core itself (the
+      // K scales sit in a ring of their own).
+      uint32_t kv_it = 0, tile_it = 0, tseq = 0, sfree_seen = 0;
       bool ok = true;
       INTFA_TDECL();
       // operand descriptors of stage 0 / K step 0; the start-address field (16-byte units) takes the offsets
       const uint64_t descQ0 = make_smem_desc(sQ, 16, C::SBO_QK, C::SWZ_QK);
       const uint64_t descK0 = make_smem_desc(sK, 16, C::SBO_QK, C::SWZ_QK);
-      // S buffer (it & 1) must be free: the caller has seen S_FREE of step it-2
-      auto issue_qk = [&](uint32_t it, bool last) -> bool {
-        const uint32_t s = it % NS, ph = (it / NS) & 1;
-        INTFA_T0();
-        if (!mbar_wait_warp(BAR(B_KFULL + s), ph, abort_flag, p.status, code_hi | PW_KF)) return false;
-        tc_fence_after();
-        INTFA_T(1);
-        INTFA_TR(2, it - 2, 6);
-        const uint64_t bd0 = descK0 + (uint64_t)(s * (C::K_BYTES >> 4));
-        const uint32_t tSb = tS + (it & 1) * G;
-        if (elect_one()) {
-          umma_f16(tSb, descArm, descArm, C::IDESC_ARM_S, 0);
-#pragma unroll
-          for (int kk = 0; kk < D / 32; ++kk) umma_i8(tSb, descQ0 + 2 * kk, bd0 + 2 * kk, C::IDESC_QK, 1);
-          umma_commit(BAR(B_SFULL + (it & 1)));
-          if (last) umma_commit(BAR(B_QEMPTY));
-        }
-        __syncwarp();
-        INTFA_T(2);
-        return true;
-      };
       while (ok) {
         const int tile = next_tile(tseq, lane == 0, true);
         if (tile < 0) break;
@@ -280,27 +275,34 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         ok = mbar_wait_warp(BAR(B_QFULL), tile_it & 1, abort_flag, p.status, code_hi | PW_QF);
         if (!ok) break;
         INTFA_T(0);
-        ok = issue_qk(kv_it, t.nsteps == 1);
-        if (ok && t.nsteps > 1) ok = issue_qk(kv_it + 1, t.nsteps == 2);
-        if (!ok) break;
         for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
-          const uint32_t s = kv_it % NS;
-          const uint32_t b = kv_it & 1;
-          // S buffer b is in the registers of its softmax group and the K scales of step j have been applied: the
-          // K stage goes back to the producer and the Q K^T two steps ahead goes into the S buffer now, long before
-          // the group needs it.  (Waited for at every step, so that the phases of the barrier stay in step.)
+          const uint32_t s = kv_it % NSK, ph = (kv_it / NSK) & 1;
+          const uint32_t sb = kv_it % NSB;
           INTFA_T0();
-          ok = mbar_wait_warp(BAR(B_SFREE + b), (kv_it >> 1) & 1, abort_flag, p.status, code_hi | PW_SFREE);
+          // every S_FREE is waited for exactly once, in step order, so the phases of the barriers stay in step
+          while (ok && sfree_seen + NSB <= kv_it) {
+            ok = mbar_wait_warp(BAR(B_SFREE + sfree_seen % NSB), (sfree_seen / NSB) & 1, abort_flag, p.status, code_hi | PW_SFREE);
+            ++sfree_seen;
+          }
           if (!ok) break;
-          tc_fence_after();
           INTFA_T(7);
           INTFA_TR(2, kv_it, 0);
-          if (elect_one()) umma_commit(BAR(B_KEMPTY + s));
-          __syncwarp();
-          if (j + 2 < t.nsteps) {
-            ok = issue_qk(kv_it + 2, j + 3 == t.nsteps);
-            if (!ok) break;
+          ok = mbar_wait_warp(BAR(B_KFULL + s), ph, abort_flag, p.status, code_hi | PW_KF);
+          if (!ok) break;
+          tc_fence_after();
+          INTFA_T(1);
+          const uint64_t bd0 = descK0 + (uint64_t)(s * (C::K_BYTES >> 4));
+          const uint32_t tSb = tS + sb * G;
+          if (elect_one()) {
+            umma_f16(tSb, descArm, descArm, C::IDESC_ARM_S, 0);
+#pragma unroll
+            for (int kk = 0; kk < D / 32; ++kk) umma_i8(tSb, descQ0 + 2 * kk, bd0 + 2 * kk, C::IDESC_QK, 1);
+            umma_commit(BAR(B_SFULL + sb));
+            umma_commit(BAR(B_KEMPTY + s));
+            if (j + 1 == t.nsteps) umma_commit(BAR(B_QEMPTY));
           }
+          __syncwarp();
+          INTFA_T(2);
           INTFA_TR(2, kv_it, 1);
         }
         ++tile_it;
@@ -323,7 +325,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (tile < 0) break;
         const TileInfo t = decode_tile<RAGGED>(p, tile, G);
         for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
-          const uint32_t s = kv_it % NS, ph = (kv_it / NS) & 1;
+          const uint32_t s = kv_it % NSV, ph = (kv_it / NSV) & 1;
           const uint32_t b = kv_it & 1;
           // P(j) written; V(j) landed; full-int8: O_j of the previous step has been read out, half-int8: the
           // accumulator has been brought to this step's running max (and the previous P V has landed in it).
@@ -336,6 +338,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             ok = mbar_wait_warp(wb, wp, abort_flag, p.status, code_hi | (w == 0 ? PW_PFULL : w == 1 ? PW_VF : PW_OFREE));
             if (!ok) break;
             if (w == 0) { INTFA_TR(2, kv_it, 2); }
+            if (w == 1) { INTFA_TR(2, kv_it, 3); }
           }
           if (!ok) break;
           tc_fence_after();
@@ -374,7 +377,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     // trace builds: timestamps of the completion of S = Q K^T of every step (role 4)
     if (p.dbg_s != nullptr && p.dbg_tile == -3 && blockIdx.x == 0) {
       for (uint32_t it = 0; it < (uint32_t)(p.dbg_step + 16); ++it) {
-        if (!mbar_wait_warp(BAR(B_SFULL + (it & 1)), (it >> 1) & 1, abort_flag, p.status, code_hi | PW_SFULL)) break;
+        if (!mbar_wait_warp(BAR(B_SFULL + it % NSB), (it / NSB) & 1, abort_flag, p.status, code_hi | PW_SFULL)) break;
         INTFA_TR(4, it, 0);
       }
     }
@@ -383,7 +386,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     reg_alloc<kPipeSoftmaxRegs>();
 #include "intfa_fwd_pipe_softmax.inc"
   } else if (warp >= 12) {
-    reg_dealloc<kPipeCorrRegs>();
+    if constexpr (kPipeCorrRegs > kPipeLaunchRegs) reg_alloc<kPipeCorrRegs>(); else reg_dealloc<kPipeCorrRegs>();
 #include "intfa_fwd_pipe_update.inc"
   }
 

@@ -332,6 +332,14 @@ __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// width-generic names for the two shapes
+__device__ __forceinline__ void tmem_ldw(uint32_t a, uint32_t (&r)[16]) { tmem_ld16(a, r); }
+__device__ __forceinline__ void tmem_ldw(uint32_t a, uint32_t (&r)[32]) { tmem_ld32(a, r); }
+__device__ __forceinline__ void tmem_ldw_wait(uint32_t (&r)[16]) { tmem_ld_wait16(r); }
+__device__ __forceinline__ void tmem_ldw_wait(uint32_t (&r)[32]) { tmem_ld_wait(r); }
+__device__ __forceinline__ void tmem_stw(uint32_t a, const uint32_t (&r)[16]) { tmem_st16(a, r); }
+__device__ __forceinline__ void tmem_stw(uint32_t a, const uint32_t (&r)[32]) { tmem_st32(a, r); }
+
 // ---------------------------------------------------------------------------
 // packed fp32x2 arithmetic (sm_100): two IEEE fp32 lanes per instruction, round-to-nearest
 // ---------------------------------------------------------------------------
