@@ -380,6 +380,26 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return r;
 }
 
+// fp16x2 fused multiply-add, one rounding per lane
+__device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+// Both halves of an fp16x2 word, each as fp32(h) + addend rounded TOWARD MINUS INFINITY (mixed-precision fma,
+// h * 1.0 + addend): with addend = 1.5*2^23 the low mantissa bits of the result are floor(h) for 0 <= h < 2^22.
+__device__ __forceinline__ void h2_floor_add(uint32_t h2, float addend, uint32_t& lo_bits, uint32_t& hi_bits) {
+  asm("{\n"
+      ".reg .b16 lo, hi, one;\n"
+      "mov.b32 {lo, hi}, %2;\n"
+      "mov.b16 one, 0x3C00;\n"
+      "fma.rm.f32.f16 %0, lo, one, %3;\n"
+      "fma.rm.f32.f16 %1, hi, one, %3;\n"
+      "}\n"
+      : "=r"(lo_bits), "=r"(hi_bits)
+      : "r"(h2), "f"(addend));
+}
+
 // ---------------------------------------------------------------------------
 // misc
 // ---------------------------------------------------------------------------
