@@ -75,7 +75,9 @@ typedef struct IntfaFwdParams {
                                    G=128 with D=64 is accepted here as a faster granularity of its own. */
   int32_t p_round;              /* 0: fp16(p)*127+0.5 truncated (Triton op); 1: fp32 p*127 RNE (CUDA path) */
   int64_t q_offset, kv_offset;  /* global position of row 0 / column 0 (ring attention); 0 otherwise */
-  /* optional outputs / carried state, all fp32 and contiguous: m,l,lse [B,H,Nq]; acc [B,H,Nq,D] */
+  /* optional outputs / carried state, all fp32 and contiguous: m,l,lse [B,H,Nq]; acc [B,H,Nq,D].
+     full-int8 with one v_scale row per (batch, head): the carried acc is in units of v_scale[ch]/127 (the
+     channel factor is applied when o is written); it is only meaningful to a later call with the same v_scale. */
   float*  lse_out;              /* log2-domain LSE  m + log2(l)  (flash_atten_int8.py:172), or NULL */
   float*  state_m; float* state_l; float* state_acc;
   int32_t state_in;             /* 1: start from (m,l,acc) in state_* instead of (-inf,1,0) */
@@ -91,6 +93,13 @@ typedef struct IntfaFwdParams {
                                    (h_h_k_ratio, csrc/flash.h:60-63, csrc/flash_fwd_kernel_full_qi8.h:141-160).
                                    0 means H.  H must be a multiple of H_kv. */
   int32_t o_dtype;              /* INTFA_OUT_*: element type of o (2 bytes either way) */
+  int32_t kv_order;             /* 0: KV tiles visited ascending (the Triton ops, flash_atten_full_int8.py:30);
+                                   1: descending, last tile first (the CUDA path's loop,
+                                   csrc/flash_fwd_kernel_full_qi8.h:331-469).  The full-int8 result depends on it. */
+  int64_t vs_stride_blk;        /* 0: v_scale is [B,H_kv,D] (or [B,H_kv] via stride 0).  Otherwise v_scale is
+                                   [B,H_kv,ceil(Nk/G),D]: one scale row per KV tile of G keys and channel, the CUDA
+                                   path's layout (csrc/flash_fwd_kernel_full_qi8.h:156-160,348,399,
+                                   csrc/mask.h:313-340); this is the element stride of the tile axis. */
 } IntfaFwdParams;
 
 /*

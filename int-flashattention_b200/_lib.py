@@ -40,6 +40,7 @@ class IntfaFwdParams(ctypes.Structure):
         ("dbg_tile", ctypes.c_int32), ("dbg_step", ctypes.c_int32),
         ("status", ctypes.c_void_p),
         ("H_kv", ctypes.c_int32), ("o_dtype", ctypes.c_int32),
+        ("kv_order", ctypes.c_int32), ("vs_stride_blk", ctypes.c_int64),
     ]
 
 

@@ -95,6 +95,10 @@ int intfa_fwd(const IntfaFwdParams* p, void* stream) {
       return set_error(INTFA_ERR_INVALID_ARG, "k_scale rows must be allocated up to the next multiple of G (%lld floats for Nk=%d)", need, p->Nk);
   }
   if (full && !p->v_scale) return set_error(INTFA_ERR_INVALID_ARG, "v_scale is NULL (full-int8)");
+  if (p->kv_order != 0 && p->kv_order != 1) return set_error(INTFA_ERR_INVALID_ARG, "kv_order must be 0 (ascending) or 1 (descending)");
+  if (p->vs_stride_blk < 0) return set_error(INTFA_ERR_INVALID_ARG, "vs_stride_blk must not be negative");
+  if (p->vs_stride_blk != 0 && (p->state_in || p->state_out))
+    return set_error(INTFA_ERR_UNSUPPORTED, "carried state with one v_scale row per KV tile is not supported");
   if (p->write_o) {
     if (!p->o) return set_error(INTFA_ERR_INVALID_ARG, "o is NULL");
     if (!aligned16(p->o) || p->o_stride[0] % 8 || p->o_stride[1] % 8 || p->o_stride[2] % 8)

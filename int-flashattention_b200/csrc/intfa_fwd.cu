@@ -80,6 +80,9 @@ __device__ __forceinline__ TileInfo decode_tile(const KParams& p, int tile, int 
   return t;
 }
 
+// KV tile visited at step j of a work item with n steps: ascending, or last tile first
+__device__ __forceinline__ int kv_tile_of_step(const KParams& p, int j, int n) { return p.kv_desc ? n - 1 - j : j; }
+
 // byte offset of 16-byte chunk `chunk` of row `row` inside a swizzled [rows][ROWB bytes] tile
 template <int ROWB>
 __device__ __forceinline__ uint32_t swz_off(int row, int chunk) {
@@ -247,13 +250,16 @@ int fwd_dispatch(const IntfaFwdParams* a, cudaStream_t stream) {
   kp.state_in = a->state_in; kp.state_out = a->state_out; kp.write_o = a->write_o;
   kp.dbg_s = a->dbg_s; kp.dbg_p = a->dbg_p; kp.dbg_tile = a->dbg_tile; kp.dbg_step = a->dbg_step;
   kp.status = a->status;
+  kp.kv_desc = a->kv_order ? 1 : 0;
+  kp.vs_sblk = a->vs_stride_blk;
   kp.MB = (a->Nq + kBM - 1) / kBM;            // the last query tile may be partial (pipelined kernel only)
   kp.num_tiles = a->B * a->H * kp.MB;
   const bool full = a->variant == INTFA_VARIANT_FULL;
   const bool rne = full && a->p_round == 1;
   const int D = a->D, G = a->G;
   // Sequence lengths that are not multiples of the tile sizes run the instantiation that masks the last tiles
-  const bool ragged = (a->Nq % kBM) != 0 || (a->Nk % a->G) != 0;
+  // (so do calls with one v_scale row per KV tile: the code for them is compiled into that instantiation only)
+  const bool ragged = (a->Nq % kBM) != 0 || (a->Nk % a->G) != 0 || a->vs_stride_blk != 0;
 #define INTFA_CASE(DD, GG)                                                                               \
   if (D == DD && G == GG) {                                                                              \
     if (full && ragged) return rne ? launch_pipe<DD, GG, true, true, true>(a, kp, stream)                \

@@ -232,19 +232,20 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           ok = mbar_wait(BAR(B_KEMPTY + s), ph ^ 1, abort_flag, p.status, code_hi | PW_KE);
           if (!ok) break;
           mbar_expect_tx(BAR(B_KFULL + s), C::K_BYTES + C::KS_BYTES);
-          tma_load_4d(sK + s * C::K_BYTES, &tmK, BAR(B_KFULL + s), 0, j * G, t.hk, t.b);
-          bulk_load_1d(sKS + (kv_it % C::NKS) * C::KS_BYTES, ks_row + j * G, C::KS_BYTES, BAR(B_KFULL + s));
+          const int jb = kv_tile_of_step(p, j, t.nsteps);
+          tma_load_4d(sK + s * C::K_BYTES, &tmK, BAR(B_KFULL + s), 0, jb * G, t.hk, t.b);
+          bulk_load_1d(sKS + (kv_it % C::NKS) * C::KS_BYTES, ks_row + jb * G, C::KS_BYTES, BAR(B_KFULL + s));
           INTFA_TR(5, kv_it, 0);
           const uint32_t sv = kv_it % NSV, phv = (kv_it / NSV) & 1;
           ok = mbar_wait(BAR(B_VEMPTY + sv), phv ^ 1, abort_flag, p.status, code_hi | PW_VE);
           if (!ok) break;
           mbar_expect_tx(BAR(B_VFULL + sv), C::V_BYTES);
           if constexpr (FULL) {
-            tma_load_4d(sV + sv * C::V_BYTES, &tmV, BAR(B_VFULL + sv), 0, j * G, t.hk, t.b);
+            tma_load_4d(sV + sv * C::V_BYTES, &tmV, BAR(B_VFULL + sv), 0, jb * G, t.hk, t.b);
           } else {
 #pragma unroll
             for (int c = 0; c < C::V_BOXES; ++c)
-              tma_load_4d(sV + sv * C::V_BYTES + c * (G * 128), &tmV, BAR(B_VFULL + sv), c * 64, j * G, t.hk, t.b);
+              tma_load_4d(sV + sv * C::V_BYTES + c * (G * 128), &tmV, BAR(B_VFULL + sv), c * 64, jb * G, t.hk, t.b);
           }
           INTFA_TR(5, kv_it, 1);
         }

@@ -86,7 +86,7 @@ def _scales_f32(s):
     return s.to(torch.float32).contiguous()
 
 
-def _fwd(variant, q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, *, G=None, p_round="triton",
+def _fwd(variant, q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, *, G=None, p_round="triton", kv_order="ascending",
          state=None, q_offset=0, kv_offset=0, return_state=False, return_lse=False, write_o=True,
          debug_tap=None, out_dtype=torch.float16):
     # shape constraints, as flash_atten_full_int8.py:189-193
@@ -138,8 +138,14 @@ def _fwd(variant, q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, *, G=Non
         elif vs.dim() == 3:                    # (B,H,D): per channel
             vs = vs.contiguous()
             P.vs_stride = _lib._i64x3(*vs.stride())
+        elif vs.dim() == 4:                    # (B,H,ceil(Nk/G),D): one row per KV tile, the CUDA path's layout
+            vs = vs.contiguous()
+            if vs.shape[2] != (Nk + G - 1) // G:
+                raise ValueError("per-tile v_scale needs ceil(Nk/G) = %d rows, got %d" % ((Nk + G - 1) // G, vs.shape[2]))
+            P.vs_stride = _lib._i64x3(vs.stride(0), vs.stride(1), vs.stride(3))
+            P.vs_stride_blk = vs.stride(2)
         else:
-            raise ValueError("v_scale must have shape (B,H) or (B,H,D)")
+            raise ValueError("v_scale must have shape (B,H), (B,H,D) or (B,H,ceil(Nk/G),D)")
         P.v_scale = vs.data_ptr()
         keep.append(vs)
     P.B, P.H, P.Nq, P.Nk, P.D = B, H, Nq, Nk, D
@@ -150,6 +156,7 @@ def _fwd(variant, q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, *, G=Non
     P.sm_scale = float(sm_scale)
     P.G = int(G)
     P.p_round = {"triton": 0, "rne": 1}[p_round]
+    P.kv_order = {"ascending": 0, "descending": 1}[kv_order]
     P.q_offset, P.kv_offset = int(q_offset), int(kv_offset)
     lse = None
     if return_lse:
@@ -196,7 +203,9 @@ def attention_full_int8(q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, **
     off-band to the on-band stage (as flash_atten_int8.py:66,157,166 does); the reference's
     full-int8 Triton kernel drops it (flash_atten_full_int8.py:71,166-179).
     Extra keyword arguments (not in the reference): G (running-max granularity, the reference's
-    BLOCK_N), p_round ("triton" | "rne"), state/q_offset/kv_offset/return_state (ring attention),
+    BLOCK_N), p_round ("triton" | "rne"), kv_order ("ascending" | "descending": the CUDA path walks the KV tiles
+    last to first, csrc/flash_fwd_kernel_full_qi8.h:331-469), v_scale of shape (B,H,ceil(Nk/G),D) (one row per KV
+    tile, the CUDA path's layout), state/q_offset/kv_offset/return_state (ring attention),
     return_lse, debug_tap, out_dtype (torch.float16 | torch.bfloat16).  k, v and their scales may have
     fewer heads than q (grouped-query attention: query head h reads K/V head h // (H // H_kv))."""
     return _fwd("full", q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, **kw)

@@ -96,14 +96,17 @@ def _imatmul(a8: torch.Tensor, b8: torch.Tensor) -> torch.Tensor:
 
 
 def int8_attention(q8, k8, v, q_scale, k_scale, v_scale, causal, sm_scale, *,
-                   variant="full", G=128, block_m=128, carry_m=True, p_round="triton",
+                   variant="full", G=128, block_m=128, carry_m=True, p_round="triton", kv_order="ascending",
                    state=None, q_offset=0, kv_offset=0, return_state=False):
     """Blockwise restatement of _attn_fwd_full_int8 / _attn_fwd_int8.
 
     q8,k8 int8 [B,H,Nq|Nk,d]; v int8 (variant "full") or fp16 ("half") [B,H,Nk,d];
     q_scale [B,H,Nq], k_scale [B,H,Nk] any float dtype (promoted to fp32 like
     flash_atten_full_int8.py:37-38); v_scale [B,H] or [B,H,d] (full only).
-    KV is visited ascending in groups of G columns (G = the reference's BLOCK_N);
+    KV is visited in groups of G columns (G = the reference's BLOCK_N), ascending like the Triton ops or, with
+    kv_order="descending", last group first like the CUDA path (csrc/flash_fwd_kernel_full_qi8.h:331-469);
+    v_scale may also be [B,H,ceil(Nk/G),d], one row per KV group, the CUDA path's layout
+    (csrc/flash_fwd_kernel_full_qi8.h:156-160, csrc/mask.h:313-340);
     `block_m` is the reference's BLOCK_M and only decides which groups use the
     masked formula when causal.  `state`=(m,l,acc) continues a previous call
     (ring attention); q_offset/kv_offset are the global positions of row 0 / col 0.
@@ -138,7 +141,9 @@ def int8_attention(q8, k8, v, q_scale, k_scale, v_scale, causal, sm_scale, *,
         vs = v_scale.to(torch.float32)
         if vs.dim() == 2:
             vs = vs[:, :, None].expand(B, H, d)
-        vs = vs[:, :, None, :]                      # [B,H,1,d]
+        if vs.dim() == 3:
+            vs = vs[:, :, None, :]                  # [B,H,1,d]: one row for every KV group
+        # else [B,H,n_groups,d]
     if state is None:
         m = torch.full((B, H, Nq), float("-inf"), dtype=torch.float32)     # :152
         l = torch.ones((B, H, Nq), dtype=torch.float32)                    # :153
@@ -173,16 +178,22 @@ def int8_attention(q8, k8, v, q_scale, k_scale, v_scale, causal, sm_scale, *,
         if full:
             p8 = _p_to_int8(p, p_round)                                    # :49-51
             tmp = _imatmul(p8, vj)                                         # :59-60
-            tmp = tmp * vs / 127                                           # :61
+            vs_j = vs if vs.shape[2] == 1 else vs[:, :, n0 // G:n0 // G + 1]
+            tmp = tmp * vs_j / 127                                         # :61
             acc_new = acc_new + tmp                                        # :62
         else:
             p16 = p.to(torch.float16)                                      # flash_atten_int8.py:58
             acc_new = acc_new + torch.matmul(p16.float(), vj.float())      # :59
         return m_new, l_new, acc_new
 
+    groups = list(range(0, Nk, G))
+    if kv_order == "descending":
+        groups.reverse()
+    elif kv_order != "ascending":
+        raise ValueError(kv_order)
     if not causal:
         rows = slice(0, Nq)
-        for n0 in range(0, Nk, G):
+        for n0 in groups:
             m, l, acc = step(rows, n0, False, m, l, acc)
     else:
         for r0 in range(0, Nq, block_m):
@@ -190,7 +201,7 @@ def int8_attention(q8, k8, v, q_scale, k_scale, v_scale, causal, sm_scale, *,
             g_lo = r0 + q_offset            # first global row of the block
             m_r, l_r, acc_r = m[:, :, rows], l[:, :, rows], acc[:, :, rows]
             m_init = m_r.clone()
-            for n0 in range(0, Nk, G):
+            for n0 in groups:
                 gc = n0 + kv_offset
                 if gc + G <= g_lo:                              # off-band, :19-20
                     m_r, l_r, acc_r = step(rows, n0, False, m_r, l_r, acc_r)

@@ -9,6 +9,8 @@ running-max granularity G is pinned to the oracle's the observed differences are
 (ex2.approx vs exp2, fma contraction, reduction order), so tighter bounds are asserted too.
 """
 import numpy as np
+import importlib
+
 import pytest
 import torch
 
@@ -295,6 +297,82 @@ def test_rne_p_rounding_mode(pkg, oracle, dev):
                                   p_round="rne")
     pkg.check_status()
     _close(oracle, out, ref)
+
+
+@pytest.mark.parametrize("variant,causal,N,G,D", [("full", False, 512, 128, 128), ("full", True, 512, 64, 128),
+                                                  ("full", True, 300, 64, 64), ("half", True, 512, 128, 128)])
+def test_kv_descending_order(variant, causal, N, G, D, pkg, oracle, dev):
+    """KV tiles visited last to first, the loop order of the reference's CUDA kernels
+    (csrc/flash_fwd_kernel_full_qi8.h:331-469), against the oracle driven with the same order; and the order
+    matters for full-int8 (the two orders differ by far more than the parity bar)."""
+    q, k, v = make_qkv(61, 1, 2, N, D)
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    v8, vs = oracle.quant_perchannel(v)
+    vv = v8 if variant == "full" else v
+    ref = oracle.int8_attention(q8, k8, vv, qs, ks, vs, causal, 0.09, variant=variant, G=G, kv_order="descending")
+    fn = pkg.attention_full_int8 if variant == "full" else pkg.attention_int8
+    args = (q8.to(dev), k8.to(dev), vv.to(dev), qs.to(dev), ks.to(dev)) + ((vs.to(dev),) if variant == "full" else ())
+    out = fn(*args, causal, 0.09, G=G, kv_order="descending")
+    pkg.check_status()
+    _close(oracle, out, ref)
+    if variant == "full" and not causal:
+        asc = fn(*args, causal, 0.09, G=G)
+        assert oracle.err_metrics(asc.cpu(), ref)["mean_rel"] > 1e-3
+
+
+@pytest.mark.parametrize("causal,N,G,D,order", [(False, 512, 64, 128, "descending"), (True, 384, 128, 128, "ascending"),
+                                                (False, 200, 64, 64, "ascending")])
+def test_v_scale_per_kv_tile(causal, N, G, D, order, pkg, oracle, dev):
+    """One V scale row per KV tile and channel, the layout of the reference's CUDA path
+    (csrc/flash_fwd_kernel_full_qi8.h:156-160,348,399; csrc/mask.h:313-340)."""
+    B, H = 1, 2
+    q, k, v = make_qkv(62, B, H, N, D)
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    nt = (N + G - 1) // G
+    vp = torch.nn.functional.pad(v, (0, 0, 0, nt * G - N)).view(B, H, nt, G, D)
+    vs = (vp.float().abs().amax(dim=3) / 127).clamp_min(1e-6)                     # [B,H,nt,D]
+    v8 = torch.round(vp.float() / vs[:, :, :, None, :]).clamp(-127, 127).to(torch.int8).view(B, H, nt * G, D)[:, :, :N].contiguous()
+    ref = oracle.attention_full_int8(q8, k8, v8, qs, ks, vs, causal, 0.09, G=G, kv_order=order)
+    out = pkg.attention_full_int8(q8.to(dev), k8.to(dev), v8.to(dev), qs.to(dev), ks.to(dev), vs.to(dev), causal, 0.09,
+                                  G=G, kv_order=order)
+    pkg.check_status()
+    _close(oracle, out, ref)
+
+
+def test_k_scale_padding_may_hold_anything(pkg, oracle, dev):
+    """Through the C ABI: Nk is not a multiple of G, so every k_scale row is allocated up to the next multiple; the
+    padding floats are filled with NaN and Inf and must not reach the result."""
+    import ctypes
+    lib_mod = importlib.import_module("int-flashattention_b200._lib")
+    lib = lib_mod.load()
+    B, H, N, D, G = 1, 2, 200, 128, 128
+    q, k, v = make_qkv(63, B, H, N, D)
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    v8, vs = oracle.quant_perchannel(v)
+    ref = oracle.attention_full_int8(q8, k8, v8, qs, ks, vs, False, 0.09, G=G)
+    Np = (N + G - 1) // G * G
+    ks_pad = torch.full((B, H, Np), float("nan"), dtype=torch.float32)
+    ks_pad[:, :, N + 1::2] = float("inf")
+    ks_pad[:, :, :N] = ks.float()
+    t = {n: x.to(dev).contiguous() for n, x in dict(q=q8, k=k8, v=v8, qs=qs.float(), ks=ks_pad, vs=vs.float()).items()}
+    o = torch.empty((B, H, N, D), dtype=torch.float16, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    P = lib_mod.IntfaFwdParams()
+    P.q, P.k, P.v, P.o = t["q"].data_ptr(), t["k"].data_ptr(), t["v"].data_ptr(), o.data_ptr()
+    P.q_scale, P.k_scale, P.v_scale = t["qs"].data_ptr(), t["ks"].data_ptr(), t["vs"].data_ptr()
+    i3, i2 = lib_mod._i64x3, lib_mod._i64x2
+    P.q_stride, P.k_stride, P.v_stride, P.o_stride = (i3(*x.stride()[:3]) for x in (t["q"], t["k"], t["v"], o))
+    P.qs_stride, P.ks_stride, P.vs_stride = i2(*t["qs"].stride()[:2]), i2(*t["ks"].stride()[:2]), i3(*t["vs"].stride())
+    P.B, P.H, P.Nq, P.Nk, P.D, P.G = B, H, N, N, D, G
+    P.variant, P.sm_scale, P.write_o, P.status = lib_mod.VARIANT_FULL, 0.09, 1, status.data_ptr()
+    lib_mod.check(lib.intfa_fwd(ctypes.byref(P), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.isfinite(o.float()).all()
+    _close(oracle, o, ref)
 
 
 def test_prologue_plus_forward(pkg, oracle, dev):
