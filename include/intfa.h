@@ -100,6 +100,11 @@ typedef struct IntfaFwdParams {
                                    [B,H_kv,ceil(Nk/G),D]: one scale row per KV tile of G keys and channel, the CUDA
                                    path's layout (csrc/flash_fwd_kernel_full_qi8.h:156-160,348,399,
                                    csrc/mask.h:313-340); this is the element stride of the tile axis. */
+  /* Test hooks for the bounded device-side waits (both 0 in normal use).  debug_wait_limit_kcycles: give up a wait
+     after this many thousand SM cycles instead of about a second.  debug_skip_k_load = n > 0: the producer leaves
+     out the K tile of the n-th KV step the CTA runs, so the wait for it runs out, the CTA drains and `status`
+     receives the wait's code -- the path a lost transfer would take. */
+  int32_t debug_wait_limit_kcycles; int32_t debug_skip_k_load;
 } IntfaFwdParams;
 
 /*

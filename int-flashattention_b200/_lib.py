@@ -41,6 +41,7 @@ class IntfaFwdParams(ctypes.Structure):
         ("status", ctypes.c_void_p),
         ("H_kv", ctypes.c_int32), ("o_dtype", ctypes.c_int32),
         ("kv_order", ctypes.c_int32), ("vs_stride_blk", ctypes.c_int64),
+        ("debug_wait_limit_kcycles", ctypes.c_int32), ("debug_skip_k_load", ctypes.c_int32),
     ]
 
 

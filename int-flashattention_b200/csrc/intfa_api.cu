@@ -6,6 +6,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "intfa_internal.h"
 
 namespace intfa {
@@ -21,17 +23,15 @@ int set_error(int code, const char* fmt, ...) {
 }
 
 int sm_count_cached() {
-  static int cache[64];
-  static bool have[64];
+  static std::atomic<int> cache[64];     // 0: not asked yet
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
-  if (!have[dev]) {
-    int n = 0;
+  int n = cache[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
-    cache[dev] = n;
-    have[dev] = true;
+    cache[dev].store(n, std::memory_order_relaxed);
   }
-  return cache[dev];
+  return n;
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -79,7 +79,7 @@ int intfa_fwd(const IntfaFwdParams* p, void* stream) {
     return set_error(INTFA_ERR_INVALID_ARG, "H=%d must be a multiple of H_kv=%d", p->H, p->H_kv);
   if (p->o_dtype != INTFA_OUT_FP16 && p->o_dtype != INTFA_OUT_BF16)
     return set_error(INTFA_ERR_INVALID_ARG, "o_dtype must be INTFA_OUT_FP16 or INTFA_OUT_BF16");
-  if ((long long)p->B * p->H * (p->Nq / 128) > 0x7fffffffLL) return set_error(INTFA_ERR_TOO_LARGE, "too many work items");
+  if ((long long)p->B * p->H * (((long long)p->Nq + 127) / 128) > 0x7fffffffLL) return set_error(INTFA_ERR_TOO_LARGE, "too many work items");
   int rc;
   if ((rc = check_tma_tensor("q", p->q, p->q_stride, 1))) return rc;
   if ((rc = check_tma_tensor("k", p->k, p->k_stride, 1))) return rc;
@@ -91,7 +91,7 @@ int intfa_fwd(const IntfaFwdParams* p, void* stream) {
     // the K scales of a KV step are fetched G at a time: every row must have room up to the next multiple of G
     const long long need = ((long long)p->Nk + p->G - 1) / p->G * p->G;
     const int hk = p->H_kv > 0 ? p->H_kv : p->H;
-    if ((hk > 1 && p->ks_stride[1] < need) || (p->B > 1 && p->ks_stride[0] < need * hk))
+    if ((hk > 1 && p->ks_stride[1] < need) || (p->B > 1 && p->ks_stride[0] < need))
       return set_error(INTFA_ERR_INVALID_ARG, "k_scale rows must be allocated up to the next multiple of G (%lld floats for Nk=%d)", need, p->Nk);
   }
   if (full && !p->v_scale) return set_error(INTFA_ERR_INVALID_ARG, "v_scale is NULL (full-int8)");

@@ -134,39 +134,41 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+static EncodeTiledFn lookup_encode_fn() {
+  void* ptr = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+      qres == cudaDriverEntryPointSuccess)
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  return nullptr;
+}
 static EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
+  static const EncodeTiledFn fn = lookup_encode_fn();     // initialised once, also when threads race to be first
   return fn;
 }
 
-// Work-item counters of the launches in flight: a small ring of words inside the library image (no
-// allocation at launch time); each launch takes the next word and zeroes it on its stream.
+// Work-item counters of the launches in flight: a ring of words inside the library image (no allocation at launch
+// time); each launch takes the next word and zeroes it on its stream.  A word comes round again after kTileCounters
+// launches of the process (all devices and streams share the cursor): a launch that is still queued or running
+// by then would have its counter zeroed under it, so at most kTileCounters launches may be in flight at a time.
+// The per-device caches below are atomics: host threads may call into the library concurrently.
 constexpr int kTileCounters = 4096;
 __device__ static unsigned int g_tile_counters[kTileCounters];
 
 static int next_tile_counter(unsigned int** out, cudaStream_t stream) {
-  static unsigned int* base[64];
-  static bool have[64];
+  static std::atomic<unsigned int*> base[64];
   static std::atomic<unsigned int> next{0};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return set_error(INTFA_ERR_CUDA, "cannot query the current device");
-  if (!have[dev]) {
+  unsigned int* b = base[dev].load(std::memory_order_acquire);
+  if (!b) {
     void* sym = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&sym, g_tile_counters);
     if (e != cudaSuccess || !sym) return set_error(INTFA_ERR_CUDA, "cudaGetSymbolAddress(tile counters): %s", cudaGetErrorString(e));
-    base[dev] = static_cast<unsigned int*>(sym);
-    have[dev] = true;
+    b = static_cast<unsigned int*>(sym);
+    base[dev].store(b, std::memory_order_release);       // every thread computes the same address
   }
-  unsigned int* c = base[dev] + (next.fetch_add(1) % kTileCounters);
+  unsigned int* c = b + (next.fetch_add(1) % kTileCounters);
   cudaError_t e = cudaMemsetAsync(c, 0, sizeof(unsigned int), stream);
   if (e != cudaSuccess) return set_error(INTFA_ERR_CUDA, "cudaMemsetAsync(tile counter): %s", cudaGetErrorString(e));
   *out = c;
@@ -210,15 +212,13 @@ static int launch_pipe(const IntfaFwdParams* a, const KParams& kp, cudaStream_t 
                         D >= 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
   }
   auto kern = intfa_fwd_pipe_kernel<D, G, FULL, PRNE, RAGGED>;
-  static bool attr_done = false;
-  static int attr_dev = -1;
+  static std::atomic<bool> attr_done[64];     // per instantiation and device (the attribute is per device)
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (!attr_done || attr_dev != dev) {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return set_error(INTFA_ERR_CUDA, "cannot query the current device");
+  if (!attr_done[dev].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) return set_error(INTFA_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_done = true;
-    attr_dev = dev;
+    attr_done[dev].store(true, std::memory_order_release);
   }
   const int sms = sm_count_cached();
   if (sms <= 0) return set_error(INTFA_ERR_CUDA, "cannot query SM count");
@@ -250,10 +250,12 @@ int fwd_dispatch(const IntfaFwdParams* a, cudaStream_t stream) {
   kp.state_in = a->state_in; kp.state_out = a->state_out; kp.write_o = a->write_o;
   kp.dbg_s = a->dbg_s; kp.dbg_p = a->dbg_p; kp.dbg_tile = a->dbg_tile; kp.dbg_step = a->dbg_step;
   kp.status = a->status;
+  kp.wait_limit_kcycles = a->debug_wait_limit_kcycles > 0 ? a->debug_wait_limit_kcycles : (1 << 21);   // default: 2^31 cycles, about a second
+  kp.skip_k_load = a->debug_skip_k_load;
   kp.kv_desc = a->kv_order ? 1 : 0;
   kp.vs_sblk = a->vs_stride_blk;
   kp.MB = (a->Nq + kBM - 1) / kBM;            // the last query tile may be partial (pipelined kernel only)
-  kp.num_tiles = a->B * a->H * kp.MB;
+  kp.num_tiles = (int)((long long)a->B * a->H * kp.MB);   // fits: intfa_fwd() has checked it
   const bool full = a->variant == INTFA_VARIANT_FULL;
   const bool rne = full && a->p_round == 1;
   const int D = a->D, G = a->G;

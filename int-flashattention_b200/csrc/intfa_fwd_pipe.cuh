@@ -151,7 +151,8 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       mbar_init(BAR(B_TDONE + i), 14);       // 2 MMA warps + 8 softmax warps + 4 accumulator warps
       mbar_init(BAR(B_AFULL + i), 4);
     }
-    *abort_flag = 0;
+    abort_flag[0] = 0;
+    abort_flag[1] = p.wait_limit_kcycles;
     mbar_init_fence();
     fence_proxy_async_smem();
   }
@@ -231,10 +232,12 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           const uint32_t s = kv_it % NSK, ph = (kv_it / NSK) & 1;
           ok = mbar_wait(BAR(B_KEMPTY + s), ph ^ 1, abort_flag, p.status, code_hi | PW_KE);
           if (!ok) break;
-          mbar_expect_tx(BAR(B_KFULL + s), C::K_BYTES + C::KS_BYTES);
           const int jb = kv_tile_of_step(p, j, t.nsteps);
-          tma_load_4d(sK + s * C::K_BYTES, &tmK, BAR(B_KFULL + s), 0, jb * G, t.hk, t.b);
-          bulk_load_1d(sKS + (kv_it % C::NKS) * C::KS_BYTES, ks_row + jb * G, C::KS_BYTES, BAR(B_KFULL + s));
+          if (p.skip_k_load == 0 || kv_it + 1 != (uint32_t)p.skip_k_load) {      // (test hook: a K tile that never arrives)
+            mbar_expect_tx(BAR(B_KFULL + s), C::K_BYTES + C::KS_BYTES);
+            tma_load_4d(sK + s * C::K_BYTES, &tmK, BAR(B_KFULL + s), 0, jb * G, t.hk, t.b);
+            bulk_load_1d(sKS + (kv_it % C::NKS) * C::KS_BYTES, ks_row + jb * G, C::KS_BYTES, BAR(B_KFULL + s));
+          }
           INTFA_TR(5, kv_it, 0);
           const uint32_t sv = kv_it % NSV, phv = (kv_it / NSV) & 1;
           ok = mbar_wait(BAR(B_VEMPTY + sv), phv ^ 1, abort_flag, p.status, code_hi | PW_VE);

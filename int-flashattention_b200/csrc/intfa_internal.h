@@ -25,6 +25,8 @@ struct KParams {
   int* dbg_s; void* dbg_p; int dbg_tile, dbg_step;
   int* status;
   int MB, num_tiles;
+  int wait_limit_kcycles;        // bounded waits give up after this many thousand SM cycles
+  int skip_k_load;               // test hook: 1-based KV step whose K tile the producer leaves out; 0: none
   int kv_desc;                   // 1: KV tiles visited last-to-first
   long long vs_sblk;             // element stride of the KV-tile axis of v_scale; 0: one scale row per (batch, head)
   unsigned int* tile_counter;    // zeroed word the CTAs draw work-item indices from

@@ -58,11 +58,11 @@ __device__ __forceinline__ uint32_t mbar_try_wait_parked(uint32_t bar, uint32_t 
   return done;
 }
 
-// Bounded wait.  Every spin in the kernels goes through here: after `kWaitLimitCycles`
-// SM cycles without completion the waiter records `code` in *status (first writer wins),
-// raises the CTA-wide abort flag and returns false; every other waiter of the CTA sees
-// the flag on its next poll and returns false as well, so the CTA drains and exits.
-constexpr long long kWaitLimitCycles = 1LL << 31;   // about one second at B200 clocks
+// Bounded wait.  Every spin in the kernels goes through here: after the limit (abort_flag[1], in units of 1024
+// SM cycles; 2^21 = about one second at B200 clocks unless a test shortens it) without completion the waiter
+// records `code` in *status (first writer wins), raises the CTA-wide abort flag (abort_flag[0]) and returns
+// false; every other waiter of the CTA sees the flag on its next look and returns false as well, so the CTA
+// drains and exits.
 constexpr uint32_t kParkNs = 20000;                 // longest single park; bounds how late an abort is seen
 
 // The abort flag and the clock are looked at every 64th poll only: the poll loop itself stays a
@@ -80,7 +80,7 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, vo
       if (*abort_flag) return false;
       const long long now = clock64();
       if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitCycles) {
+      if (now - t0 > ((long long)abort_flag[1] << 10)) {
         *abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;

@@ -18,6 +18,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "intfa_internal.h"
 
 namespace intfa {
@@ -325,25 +327,25 @@ int quant_v(const void* v, const int64_t* st, void* v8, float* scale, int mode, 
 __device__ __align__(256) static unsigned int g_static_colmax[kStaticColmaxWords];
 
 static unsigned int* static_colmax_ptr(int* rc) {
-  static unsigned int* ptr[64];
-  static bool have[64];
+  static std::atomic<unsigned int*> ptr[64];     // host threads may race to be first: each stores the same address
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
     *rc = set_error(INTFA_ERR_CUDA, "cannot query the current device");
     return nullptr;
   }
-  if (!have[dev]) {
+  unsigned int* q = ptr[dev].load(std::memory_order_acquire);
+  if (!q) {
     void* sym = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&sym, g_static_colmax);     // with device `dev` current
     if (e != cudaSuccess || sym == nullptr) {
       *rc = set_error(INTFA_ERR_CUDA, "cudaGetSymbolAddress(static colmax scratch): %s", cudaGetErrorString(e));
       return nullptr;
     }
-    ptr[dev] = static_cast<unsigned int*>(sym);
-    have[dev] = true;
+    q = static_cast<unsigned int*>(sym);
+    ptr[dev].store(q, std::memory_order_release);
   }
   *rc = INTFA_OK;
-  return ptr[dev];
+  return q;
 }
 
 int quant_v_static(const void* v, const int64_t* st, void* v8, float* scale, int mode, int B, int H, int N, int D,

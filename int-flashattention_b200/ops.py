@@ -81,14 +81,15 @@ def _scales_f32(s):
     if s.dtype == torch.float16:
         src = s.contiguous()
         dst = torch.empty(src.shape, dtype=torch.float32, device=s.device)
-        _lib.check(_lib.load().intfa_scales_f16_to_f32(src.data_ptr(), dst.data_ptr(), src.numel(), _stream(s)))
+        with torch.cuda.device(s.device):      # the library launches on the current device
+            _lib.check(_lib.load().intfa_scales_f16_to_f32(src.data_ptr(), dst.data_ptr(), src.numel(), _stream(s)))
         return dst
     return s.to(torch.float32).contiguous()
 
 
 def _fwd(variant, q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, *, G=None, p_round="triton", kv_order="ascending",
          state=None, q_offset=0, kv_offset=0, return_state=False, return_lse=False, write_o=True,
-         debug_tap=None, out_dtype=torch.float16):
+         debug_tap=None, out_dtype=torch.float16, debug_wait=None):
     # shape constraints, as flash_atten_full_int8.py:189-193
     HEAD_DIM_Q, HEAD_DIM_K, HEAD_DIM_V = q.shape[-1], k.shape[-1], v.shape[-1]
     assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V
@@ -183,6 +184,8 @@ def _fwd(variant, q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, *, G=Non
         dbg_p = torch.zeros((128, G), dtype=torch.int8 if full else torch.float16, device=q.device)
         P.dbg_s, P.dbg_p, P.dbg_tile, P.dbg_step = dbg_s.data_ptr(), dbg_p.data_ptr(), int(tile), int(step)
         dbg = (dbg_s, dbg_p)
+    if debug_wait is not None:                 # test hooks of the bounded waits: (limit in kilo-cycles, K step to leave out)
+        P.debug_wait_limit_kcycles, P.debug_skip_k_load = int(debug_wait[0]), int(debug_wait[1])
     P.status = _status_word(q.device).data_ptr()
     with torch.cuda.device(q.device):
         _lib.check(lib.intfa_fwd(ctypes.byref(P), _stream(q)))

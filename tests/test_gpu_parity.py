@@ -594,3 +594,24 @@ def test_head_dim_32(variant, G, N, causal, pkg, oracle, dev):
 
 def test_status_word_clean(pkg, dev):
     assert pkg.check_status(dev) == 0
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_next_call_works(pkg, oracle, dev):
+    """The producer leaves out one K tile (test hook), so the MMA warp's wait for it runs out after the shortened
+    limit: the kernel must RETURN, the status word must carry the wait's code, check_status must raise
+    ERR_DEVICE_WAIT -- and the context must be fine for the next, ordinary call."""
+    lib_mod = importlib.import_module("int-flashattention_b200._lib")
+    ops = importlib.import_module("int-flashattention_b200.ops")
+    q, k, v = make_qkv(64, 1, 1, 256, 128)
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    v8, vs = oracle.quant_perchannel(v)
+    args = (q8.to(dev), k8.to(dev), v8.to(dev), qs.to(dev), ks.to(dev), vs.to(dev), False, 0.09)
+    pkg.check_status()
+    ops._fwd("full", *args, debug_wait=(2000, 1))          # give up after 2 M cycles (about 1 ms); K tile of step 1 never comes
+    with pytest.raises(lib_mod.IntfaError) as ei:
+        pkg.check_status()
+    assert ei.value.code == lib_mod.ERR_DEVICE_WAIT
+    out = pkg.attention_full_int8(*args)
+    assert pkg.check_status() == 0
+    _close(oracle, out, oracle.attention_full_int8(q8, k8, v8, qs, ks, vs, False, 0.09))
