@@ -42,6 +42,17 @@ WORKLOADS = {
 }
 DEFAULT_WORKLOAD = "c2_full_b4_h32_n8192_d128"
 METRIC = "INT8 attn fwd effective TOPS (4*B*H*N^2*d / t, halved for causal), prologue included"
+LAUNCHES_PROLOGUE_FULL = 4      # kernels of the quantisation prologue per step: per-token Q, per-token K, V column absmax, V quantise
+LAUNCHES_PROLOGUE_HALF = 2      # per-token Q, per-token K
+
+
+def config_of(workload):
+    """The `config` object of the JSON line -- the same for this arm and the reference arm."""
+    variant, B, H, N, D, causal, std, outlier = WORKLOADS[workload]
+    return {"workload": workload, "variant": variant, "B_per_gpu": B, "H": H, "N": N, "D": D, "causal": causal,
+            "sm_scale": D ** -0.5, "quantised_in_step": True,
+            "l2": "inputs exceed L2 (%.0f MiB of fp16 Q/K/V per step)" % (3 * B * H * N * D * 2 / 2 ** 20),
+            "sharding": "batch x heads, no collective"}
 
 
 def attn_ops(B, H, N, D, causal):
@@ -172,24 +183,21 @@ def run_reference_arm(args, rank, world):
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": args.gpus,
             "steps": len(vals), "warmup": 1, "ms_per_step": 1e3 * dt / len(vals), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "s8", "data": "synthetic",
-            "config": {"workload": args.workload, "variant": variant, "B": B, "H": H, "N": N, "D": D, "causal": causal,
-                       "note": "each step = bounded sample of whole (batch,head) slices on host cores"},
+            "config": config_of(args.workload),
+            "note": "each step = a bounded sample of whole (batch,head) slices of the workload on the host cores",
             "cpu_baseline": {"value": value, "unit": "TOPS", "cores": base["cores"], "kind": "port",
                              "sample": vals[0]["sample"]},
             "e2e": {"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
-def run_ring(args, pkg, dist, rank, world, local_rank, dev):
+def measure_ring(pkg, dist, rank, world, local_rank, dev, workload, steps, warmup, prefetch=None):
     """Long-context causal full-int8 attention, sequence sharded zigzag over the ranks: every rank owns
     half-chunks (rank, 2*world-1-rank) of the global sequence, quantises them (per-channel V absmax
     all-reduced), and runs the ascending ring (int8 K/V + fp32 K scales by NCCL send/recv).  A step =
-    prologue + ring forward of the whole sequence; strong scaling (the global problem is fixed)."""
-    variant, B, H, N, D, causal, std, outlier = WORKLOADS[args.workload]
-    if world < 2:
-        if rank == 0:
-            print(json.dumps({"metric": METRIC, "unavailable": "the ring workload needs --gpus >= 2"}), flush=True)
-        return
+    prologue + ring forward of the whole sequence; strong scaling (the global problem is fixed).
+    Returns (ms per step as the max over ranks, clocks of rank 0 or None, half-chunk rows)."""
+    variant, B, H, N, D, causal, std, outlier = WORKLOADS[workload]
     nh = N // (2 * world)
     sm_scale = D ** -0.5
     parts = []
@@ -197,19 +205,19 @@ def run_ring(args, pkg, dist, rank, world, local_rank, dev):
         g = torch.Generator(device=dev).manual_seed(5000 + c)
         parts.append([std * torch.randn(B, H, nh, D, device=dev, generator=g, dtype=torch.float32) for _ in range(3)])
     q, k, v = (torch.cat([parts[0][i], parts[1][i]], dim=2).half() for i in range(3))
+    del parts
 
     def step():
         q8, qs = pkg.quant_pertoken(q)
         k8, ks = pkg.quant_pertoken(k)
         v8, vs = pkg.shard.quantize_v_global(v, "per_channel")
-        return pkg.shard.ring_attention_causal(q8, k8, v8, qs, ks, vs, sm_scale, variant="full")
+        return pkg.shard.ring_attention_causal(q8, k8, v8, qs, ks, vs, sm_scale, variant="full", prefetch=prefetch)
 
     def barrier():
         dist.barrier(device_ids=[local_rank])
         torch.cuda.synchronize(dev)
 
-    steps = min(args.steps, 10)
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
     pkg.check_status(dev)
     sampler = ClockSampler(local_rank)
@@ -226,10 +234,131 @@ def run_ring(args, pkg, dist, rank, world, local_rank, dev):
     pkg.check_status(dev)
     t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t[0])
+    return float(t[0]), clocks, nh
+
+
+def ring_self_check(pkg, dist, rank, world, local_rank, dev):
+    """Small ring run (2048 tokens per rank) whose local output must equal, bit for bit, the same rows of a
+    single-device causal pass over the whole sequence computed on this rank.  Returns "bit-equal" or a
+    description of the mismatch, the same on every rank."""
+    B, H, D = 1, 4, 128
+    N = 2048 * world
+    g = torch.Generator(device=dev).manual_seed(777)          # same tensors on every rank
+    q, k, v = (0.5 * torch.randn(B, H, N, D, device=dev, generator=g, dtype=torch.float32) for _ in range(3))
+    q, k, v = q.half(), k.half(), v.half()
+    sp = lambda t: pkg.shard.zigzag_split(t, world, rank).contiguous()
+    q8, qs = pkg.quant_pertoken(sp(q))
+    k8, ks = pkg.quant_pertoken(sp(k))
+    v8, vs = pkg.shard.quantize_v_global(sp(v), "per_channel")
+    loc = pkg.shard.ring_attention_causal(q8, k8, v8, qs, ks, vs, 0.09, variant="full")
+    fq8, fqs = pkg.quant_pertoken(q)
+    fk8, fks = pkg.quant_pertoken(k)
+    fv8, fvs = pkg.quant_perchannel(v)
+    one = pkg.attention_full_int8(fq8, fk8, fv8, fqs, fks, fvs, True, 0.09)
+    pkg.check_status(dev)
+    want = sp(one)
+    bad = torch.tensor([0 if torch.equal(loc, want) else 1, 0 if torch.equal(v8, sp(fv8)) else 1], device=dev, dtype=torch.int32)
+    dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+    if int(bad[0]) == 0 and int(bad[1]) == 0:
+        return "bit-equal"
+    return "MISMATCH (output %d, sharded V quantisation %d)" % (int(bad[0]), int(bad[1]))
+
+
+def measure_c4_strong(pkg, dist, rank, world, local_rank, dev, steps, warmup):
+    """Full-int8 B64 H64 N4096 d128 non-causal, the (batch, head) pairs split evenly over the ranks
+    (shard.bh_slice), no collective: strong scaling of a fixed global problem.  Returns ms per step (max over ranks)."""
+    B, H, N, D = 64, 64, 4096, 128
+    dim, s0, s1 = pkg.shard.bh_slice(B, H, world, rank)
+    Bl, Hl = (s1 - s0, H) if dim == 0 else (1, s1 - s0)
+    q, k, v = synth(Bl, Hl, N, D, 1.0, False, 3000 + rank, dev)
+    sm_scale = D ** -0.5
+
+    def step():
+        return pkg.int_flash_attention(q, k, v, False, sm_scale, variant="full")
+
+    for _ in range(warmup):
+        step()
+    pkg.check_status(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier(device_ids=[local_rank])
+    torch.cuda.synchronize(dev)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    dist.barrier(device_ids=[local_rank])
+    torch.cuda.synchronize(dev)
+    pkg.check_status(dev)
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0])
+
+
+def int8_peak_tops(peaks):
+    """Denominator of the tensor roofline: the int8 GEMM rate measured on this pool (profiles/roofline_inputs.json,
+    from `--workload int8_peak`), else twice the measured bf16 burst rate."""
+    pj = os.path.join(ROOT, "profiles", "roofline_inputs.json")
+    try:
+        m = json.load(open(pj)).get("int8_peak", {})
+        if m.get("burst_tops"):
+            # the attention kernel is timed per launch inside a region of a fraction of a second, at full clocks:
+            # the burst figure is the like-for-like denominator
+            return float(m["burst_tops"]), "library int8 GEMM (torch._int_mm 8192^3, burst) measured on this pool"
+    except Exception:
+        pass
+    return 2.0 * peaks["bf16_tflops"], "2 x MEASURED_PEAKS.bf16_tflops (burst; int8 dense rate = 2x bf16)"
+
+
+def run_int8_peak(dev):
+    """Library int8 GEMM rate (torch._int_mm, cuBLASLt): burst = best of 10 single calls, sustained = a 3 s loop.
+    Only a yardstick for the roofline denominator; no product path calls it."""
+    n = 8192
+    a = torch.randint(-127, 128, (n, n), device=dev, dtype=torch.int8)
+    b = torch.randint(-127, 128, (n, n), device=dev, dtype=torch.int8)
+    for _ in range(5):
+        torch._int_mm(a, b)
+    torch.cuda.synchronize(dev)
+    best = 1e9
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        torch._int_mm(a, b)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        best = min(best, e0.elapsed_time(e1))
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    reps, total_ms, calls = 50, 0.0, 0
+    t0 = time.perf_counter()
+    while time.perf_counter() - t0 < 3.0:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            torch._int_mm(a, b)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        total_ms += e0.elapsed_time(e1)
+        calls += reps
+    clocks = sampler.stop()
+    ops = 2.0 * n ** 3
+    print(json.dumps({"workload": "int8_peak", "how": "torch._int_mm 8192^3 (library kernel, not part of any product path)",
+                      "burst_tops": ops / (best * 1e-3) / 1e12, "sustained_tops": ops * calls / (total_ms * 1e-3) / 1e12,
+                      "clocks": clocks}), flush=True)
+
+
+def run_ring(args, pkg, dist, rank, world, local_rank, dev):
+    variant, B, H, N, D, causal, std, outlier = WORKLOADS[args.workload]
+    if world < 2:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "unavailable": "the ring workload needs --gpus >= 2"}), flush=True)
+        return
+    steps = min(args.steps, 10)
+    ms, clocks, nh = measure_ring(pkg, dist, rank, world, local_rank, dev, args.workload, steps, args.warmup)
+    check = ring_self_check(pkg, dist, rank, world, local_rank, dev)
     ops = attn_ops(B, H, N, D, True)
     if rank == 0:
         peaks, src = measured_peaks()
+        peak, peak_src = int8_peak_tops(peaks)
         value = ops / (ms * 1e-3) / 1e12
         kv_bytes = B * H * nh * (2 * D + 4)           # one int8 K + V half-chunk and its fp32 K scales
         line = {"metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": world, "steps": steps, "warmup": args.warmup,
@@ -239,12 +368,10 @@ def run_ring(args, pkg, dist, rank, world, local_rank, dev):
                            "causal": True, "layout": "zigzag half-chunks, ascending ring, NCCL send/recv",
                            "half_chunk_rows": nh, "bytes_per_half_chunk_transfer": kv_bytes,
                            "l2": "inputs exceed L2"},
-                "clocks": clocks, "gpu_launches": steps * (5 + 2 * world + 1),
-                "roofline": {"bound": "tensor", "kernel": "intfa_fwd_pipe_kernel" if (variant == "full" or D == 128) else "intfa_fwd_kernel",
-                             "achieved": value / world,
-                             "peak": 2.0 * peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
-                             "frac": value / world / (2.0 * peaks["bf16_tflops_sustained"]), "traffic": None,
-                             "peak_source": "per GPU; 2 x MEASURED_PEAKS.bf16_tflops_sustained (%s)" % src},
+                "clocks": clocks, "gpu_launches": steps * (LAUNCHES_PROLOGUE_FULL + 2 * world + 1), "ring_check": check,
+                "roofline": {"bound": "tensor", "kernel": "intfa_fwd_pipe_kernel", "achieved": value / world,
+                             "peak": peak, "unit": "TFLOP/s", "frac": value / world / peak, "traffic": None,
+                             "peak_source": "per GPU; " + peak_src},
                 "e2e": None, "cpu_baseline": None}
         print(json.dumps(line), flush=True)
 
@@ -255,9 +382,10 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + ["int8_peak"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-multi", action="store_true", help="with --gpus >= 2: skip the ring and strong-scaling sub-measurements")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -277,6 +405,12 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
+    if args.workload == "int8_peak":
+        if rank == 0:
+            run_int8_peak(dev)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     variant, B, H, N, D, causal, std, outlier = WORKLOADS[args.workload]
     full = variant == "full"
     sm_scale = D ** -0.5
@@ -332,7 +466,7 @@ def main():
     ms_per_step = ms_total / args.steps
     ops_step = attn_ops(B, H, N, D, causal)
     value = ops_step * world / (ms_per_step * 1e-3) / 1e12
-    launches_per_step = 5 if full else 3            # 2x per-token quant (+ V colmax + V quant) + attention
+    launches_per_step = (LAUNCHES_PROLOGUE_FULL if full else LAUNCHES_PROLOGUE_HALF) + 1      # prologue + attention
 
     # ---- end-to-end through the public API with HOST buffers (pinned): H2D of q,k,v and D2H of o every step
     e2e = None
@@ -391,19 +525,45 @@ def main():
                "serial_value": ops_step * world / (float(te[1]) * 1e-3) / 1e12, "serial_ms_per_step": float(te[1])}
         del hq, hk, hv, hin, hout, pipe
 
+    # ---- with 2 or more GPUs, and on the default workload: the two multi-GPU decompositions as sub-objects of the line
+    multi = {}
+    if world > 1 and args.workload == DEFAULT_WORKLOAD and not args.no_multi:
+        del q, k, v, o
+        torch.cuda.empty_cache()
+        rw = "c5_ring_full_b1_h32_n131072_d128_causal"
+        r_ms, _, r_nh = measure_ring(pkg, dist, rank, world, local_rank, dev, rw, steps=4, warmup=2)
+        torch.cuda.empty_cache()
+        multi["ring_check"] = ring_self_check(pkg, dist, rank, world, local_rank, dev)
+        c4_ms = measure_c4_strong(pkg, dist, rank, world, local_rank, dev, steps=3, warmup=1)
+        torch.cuda.empty_cache()
+        r_ops = attn_ops(1, 32, 131072, 128, True)
+        c4_ops = attn_ops(64, 64, 4096, 128, False)
+        multi["ring"] = {"workload": rw, "value": r_ops / (r_ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": r_ms,
+                         "per_gpu": r_ops / (r_ms * 1e-3) / 1e12 / world, "scaling": "strong", "half_chunk_rows": r_nh,
+                         "transport": "NCCL send/recv of int8 K/V + fp32 K scales into local HBM, all transfers posted up front"}
+        multi["c4_strong"] = {"workload": "full-int8 B64 H64 N4096 d128 non-causal, (batch, head) pairs split over the ranks",
+                              "value": c4_ops / (c4_ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": c4_ms,
+                              "per_gpu": c4_ops / (c4_ms * 1e-3) / 1e12 / world, "scaling": "strong", "collective": "none"}
+
     if rank == 0:
         peaks, src = measured_peaks()
-        peak_int8 = 2.0 * peaks["bf16_tflops_sustained"]
+        peak_int8, peak_src = int8_peak_tops(peaks)
+        for kname in ("ring", "c4_strong"):
+            if kname in multi:
+                multi[kname]["frac"] = multi[kname]["per_gpu"] / peak_int8
         achieved = ops_step / (attn_ms * 1e-3) / 1e12
         prof = {}
         pj = os.path.join(ROOT, "profiles", "roofline_inputs.json")
         if os.path.exists(pj):
             prof = json.load(open(pj)).get(args.workload, {})
-        roofline = {"bound": "tensor", "kernel": "intfa_fwd_pipe_kernel" if (full or D == 128) else "intfa_fwd_kernel",
+        roofline = {"bound": "tensor", "kernel": "intfa_fwd_pipe_kernel",
                     "achieved": achieved, "peak": peak_int8,
                     "unit": "TFLOP/s", "frac": achieved / peak_int8,
+                    "frac_of_2x_bf16_burst": achieved / (2.0 * peaks["bf16_tflops"]),
+                    "frac_of_2x_bf16_sustained": achieved / (2.0 * peaks["bf16_tflops_sustained"]),
                     "traffic": prof.get("attn_dram_bytes_per_launch"),
-                    "peak_source": "2 x MEASURED_PEAKS.bf16_tflops_sustained (%s; int8 dense rate = 2x bf16)" % src,
+                    "traffic_source": "constant from an earlier one-pass ncu capture of this launch (profiles/), not measured by this run",
+                    "peak_source": peak_src + " (MEASURED_PEAKS: %s)" % src,
                     "kernel_ms": attn_ms,
                     "prologue": {"bound": "hbm", "ms": ms_per_step - attn_ms,
                                  "achieved": prologue_bytes(B, H, N, D, full) / ((ms_per_step - attn_ms) * 1e-3) / 1e9,
@@ -415,13 +575,11 @@ def main():
         line = {"metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "s8", "data": "synthetic",
-                "config": {"workload": args.workload, "variant": variant, "B_per_gpu": B, "H": H, "N": N, "D": D,
-                           "causal": causal, "sm_scale": sm_scale, "quantised_in_step": True,
-                           "l2": "inputs exceed L2 (%.0f MiB of fp16 Q/K/V per step)" % (3 * q.numel() * 2 / 2 ** 20),
-                           "sharding": "batch x heads, no collective"},
+                "config": config_of(args.workload),
                 "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
                 "roofline": roofline, "cpu_baseline": cpu,
                 "pct_of_nominal_int8_peak": 100.0 * achieved / 4500.0}
+        line.update(multi)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
