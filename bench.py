@@ -42,8 +42,8 @@ WORKLOADS = {
 }
 DEFAULT_WORKLOAD = "c2_full_b4_h32_n8192_d128"
 METRIC = "INT8 attn fwd effective TOPS (4*B*H*N^2*d / t, halved for causal), prologue included"
-LAUNCHES_PROLOGUE_FULL = 4      # kernels of the quantisation prologue per step: per-token Q, per-token K, V column absmax, V quantise
-LAUNCHES_PROLOGUE_HALF = 2      # per-token Q, per-token K
+LAUNCHES_PROLOGUE_FULL = 2      # kernels of the quantisation prologue per step: Q rows + K rows + V column absmax in one grid; V quantise
+LAUNCHES_PROLOGUE_HALF = 1      # Q rows + K rows in one grid
 
 
 def config_of(workload):
@@ -368,7 +368,7 @@ def run_ring(args, pkg, dist, rank, world, local_rank, dev):
                            "causal": True, "layout": "zigzag half-chunks, ascending ring, NCCL send/recv",
                            "half_chunk_rows": nh, "bytes_per_half_chunk_transfer": kv_bytes,
                            "l2": "inputs exceed L2"},
-                "clocks": clocks, "gpu_launches": steps * (LAUNCHES_PROLOGUE_FULL + 2 * world + 1), "ring_check": check,
+                "clocks": clocks, "gpu_launches": steps * (5 + 2 * world + 1), "ring_check": check,
                 "roofline": {"bound": "tensor", "kernel": "intfa_fwd_pipe_kernel", "achieved": value / world,
                              "peak": peak, "unit": "TFLOP/s", "frac": value / world / peak, "traffic": None,
                              "peak_source": "per GPU; " + peak_src},
@@ -443,13 +443,12 @@ def main():
     barrier()
     ev0.record()
     for i in range(args.steps):
-        q8, qs = pkg.quant_pertoken(q)
-        k8, ks = pkg.quant_pertoken(k)
         if full:
-            v8, vs = pkg.quant_perchannel(v)
+            q8, qs, k8, ks, v8, vs = pkg.quant_qkv(q, k, v)
             a0[i].record()
             o = pkg.attention_full_int8(q8, k8, v8, qs, ks, vs, causal, sm_scale)
         else:
+            q8, qs, k8, ks = pkg.quant_qkv(q, k)
             a0[i].record()
             o = pkg.attention_int8(q8, k8, v, qs, ks, causal, sm_scale)
         a1[i].record()

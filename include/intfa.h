@@ -159,6 +159,22 @@ int intfa_v_quant_from_colmax(const void* v, const int64_t v_stride[3], const vo
                               int32_t B, int32_t H, int32_t N, int32_t D, void* stream);
 
 /*
+ * The whole quantisation prologue of one attention call in TWO launches and no memset: the first quantises the rows
+ * of q and of k per token (as intfa_quant_pertoken) and, in the same grid, takes the column absmax of v chunk by
+ * chunk into `workspace` (partial maxima, plain stores -- nothing to clear); the second quantises v (as
+ * intfa_quant_v).  Results are bit-identical to the separate entry points.
+ * Replaces: quant_pertoken(q), quant_pertoken(k), quant_pertensor(v) as benchmark.py:158-160 calls them in a row.
+ * q [B,H,Nq,D] and k [B,H_kv,Nk,D]: fp16, CONTIGUOUS; v [B,H_kv,Nk,D]: fp16 with element strides for (B,H,N), or
+ * NULL (half-int8: V stays fp16) -- then v8, v_scale, workspace are not used.  `workspace`: device scratch of
+ * intfa_quant_qkv_workspace_bytes() bytes, contents irrelevant.
+ */
+size_t intfa_quant_qkv_workspace_bytes(int32_t B, int32_t H_kv, int32_t Nk, int32_t D);
+int intfa_quant_qkv(const void* q, const void* k, const void* v, const int64_t v_stride[3],
+                    void* q8, void* k8, void* v8, float* q_scale, float* k_scale, float* v_scale, int32_t v_mode,
+                    int32_t B, int32_t H, int32_t H_kv, int32_t Nq, int32_t Nk, int32_t D,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * intfa_quant_v for callers that cannot allocate device memory.
  * No counterpart in the reference (its quantisers are PyTorch expressions that allocate freely).
  *

@@ -14,7 +14,8 @@ VARIANT_FULL, VARIANT_HALF = 0, 1
 VSCALE_PER_TENSOR, VSCALE_PER_CHANNEL = 0, 1
 
 EXPORTS = ("intfa_version", "intfa_last_error", "intfa_fwd", "intfa_quant_pertoken",
-           "intfa_quant_v_workspace_bytes", "intfa_quant_v", "intfa_v_colmax", "intfa_v_quant_from_colmax", "intfa_quant_v_static",
+           "intfa_quant_v_workspace_bytes", "intfa_quant_v", "intfa_quant_qkv_workspace_bytes", "intfa_quant_qkv",
+           "intfa_v_colmax", "intfa_v_quant_from_colmax", "intfa_quant_v_static",
            "intfa_quant_v_static_max_words", "intfa_scales_f16_to_f32", "intfa_sm_count")
 
 _i64x3 = ctypes.c_int64 * 3
@@ -77,6 +78,11 @@ def load():
     lib.intfa_quant_v_workspace_bytes.argtypes = [i32, i32, i32]
     lib.intfa_quant_v.restype = ctypes.c_int
     lib.intfa_quant_v.argtypes = [vp, ctypes.POINTER(i64), vp, vp, i32, i32, i32, i32, i32, vp, ctypes.c_size_t, vp]
+    lib.intfa_quant_qkv_workspace_bytes.restype = ctypes.c_size_t
+    lib.intfa_quant_qkv_workspace_bytes.argtypes = [i32, i32, i32, i32]
+    lib.intfa_quant_qkv.restype = ctypes.c_int
+    lib.intfa_quant_qkv.argtypes = [vp, vp, vp, ctypes.POINTER(i64), vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
+                                    vp, ctypes.c_size_t, vp]
     lib.intfa_v_colmax.restype = ctypes.c_int
     lib.intfa_v_colmax.argtypes = [vp, ctypes.POINTER(i64), vp, i32, i32, i32, i32, vp]
     lib.intfa_v_quant_from_colmax.restype = ctypes.c_int

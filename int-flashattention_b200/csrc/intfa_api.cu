@@ -150,6 +150,33 @@ int intfa_quant_v(const void* v, const int64_t v_stride[3], void* v8, float* sca
   return quant_v(v, v_stride, v8, scale, mode, B, H, N, D, workspace, reinterpret_cast<cudaStream_t>(stream));
 }
 
+size_t intfa_quant_qkv_workspace_bytes(int32_t B, int32_t H_kv, int32_t Nk, int32_t D) {
+  if (B <= 0 || H_kv <= 0 || Nk <= 0 || D <= 0) return 0;
+  return quant_qkv_workspace_bytes(B, H_kv, Nk, D);
+}
+
+int intfa_quant_qkv(const void* q, const void* k, const void* v, const int64_t v_stride[3], void* q8, void* k8, void* v8,
+                    float* q_scale, float* k_scale, float* v_scale, int32_t v_mode, int32_t B, int32_t H, int32_t H_kv,
+                    int32_t Nq, int32_t Nk, int32_t D, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!q || !k || !q8 || !k8 || !q_scale || !k_scale) return set_error(INTFA_ERR_INVALID_ARG, "NULL argument");
+  if (B <= 0 || H <= 0 || H_kv <= 0 || Nq <= 0 || Nk <= 0) return set_error(INTFA_ERR_INVALID_ARG, "B, H, H_kv, Nq, Nk must be positive");
+  if (D != 32 && D != 64 && D != 128) return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: 32, 64 or 128", D);
+  if (!aligned16(q) || !aligned16(k) || !aligned16(q8) || !aligned16(k8))
+    return set_error(INTFA_ERR_INVALID_ARG, "q, k, q8, k8 must be 16-byte aligned (and contiguous)");
+  if (v) {
+    if (!v_stride || !v8 || !v_scale) return set_error(INTFA_ERR_INVALID_ARG, "v given without v_stride / v8 / v_scale");
+    if (!aligned16(v) || !aligned16(v8) || v_stride[0] % 8 || v_stride[1] % 8 || v_stride[2] % 8)
+      return set_error(INTFA_ERR_INVALID_ARG, "v rows must be 16-byte aligned (pointer and strides multiples of 8 elements)");
+    if (v_mode != INTFA_VSCALE_PER_TENSOR && v_mode != INTFA_VSCALE_PER_CHANNEL)
+      return set_error(INTFA_ERR_INVALID_ARG, "v_mode must be INTFA_VSCALE_PER_TENSOR or INTFA_VSCALE_PER_CHANNEL");
+    if ((long long)B * H_kv > 65535) return set_error(INTFA_ERR_TOO_LARGE, "B*H_kv=%lld exceeds 65535", (long long)B * H_kv);
+    if (!workspace || workspace_bytes < quant_qkv_workspace_bytes(B, H_kv, Nk, D))
+      return set_error(INTFA_ERR_INVALID_ARG, "workspace missing or smaller than intfa_quant_qkv_workspace_bytes()");
+  }
+  return quant_qkv(q, k, v, v_stride, q8, k8, v8, q_scale, k_scale, v_scale, v_mode, B, H, H_kv, Nq, Nk, D, workspace,
+                   reinterpret_cast<cudaStream_t>(stream));
+}
+
 int intfa_v_colmax(const void* v, const int64_t v_stride[3], void* colmax, int32_t B, int32_t H, int32_t N, int32_t D,
                    void* stream) {
   if (!v || !v_stride || !colmax) return set_error(INTFA_ERR_INVALID_ARG, "NULL argument");

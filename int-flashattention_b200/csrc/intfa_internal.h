@@ -48,6 +48,10 @@ int v_quant_from_colmax(const void* v, const int64_t* st, const void* colmax, vo
 constexpr int kStaticColmaxWords = 65536;   // 256 KiB: built-in scratch of intfa_quant_v_static (B*H*D limit)
 int quant_v_static(const void* v, const int64_t* st, void* v8, float* scale, int mode, int B, int H, int N, int D,
                    cudaStream_t stream);
+size_t quant_qkv_workspace_bytes(int B, int Hkv, int Nk, int D);
+int quant_qkv(const void* q, const void* k, const void* v, const int64_t* v_st, void* q8, void* k8, void* v8, float* qs,
+              float* ks, float* vs, int mode, int B, int H, int Hkv, int Nq, int Nk, int D, void* workspace,
+              cudaStream_t stream);
 int scales_f16_to_f32(const void* src, float* dst, long long n, cudaStream_t stream);
 
 }  // namespace intfa

@@ -12,8 +12,9 @@
 //
 // Each row of D fp16 is read by D/8 lanes with one 128-bit load per lane; the row/column
 // maxima are reduced with warp shuffles.  Per-token: one pass.  V (per-channel or
-// per-(batch,head)): a column-absmax pass into a small scratch array (atomicMax on the
-// bit pattern of non-negative floats), then the quantising pass.
+// per-(batch,head)): a column-absmax pass, then the quantising pass.  The fused entry (quant_qkv) runs the Q rows,
+// the K rows and the V column-absmax pass as ONE launch (partial maxima per chunk, plain stores) and the V
+// quantising pass as a second; the stand-alone V entries use atomicMax into a small scratch array instead.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -72,17 +73,17 @@ __device__ __forceinline__ void st_stream(void* p, uint2 v) {
 
 constexpr int kQuantUnroll = 4;    // independent 128-bit loads in flight per lane
 
+// Per-token quantisation of the rows that CTA `cta` of `ncta` owns (a grid-stride loop over groups of rows).
 template <int D, bool CONTIG>
-__global__ void __launch_bounds__(256) quant_pertoken_kernel(const __half* __restrict__ x, long long sB, long long sH,
-                                                             long long sN, int8_t* __restrict__ x8,
-                                                             float* __restrict__ scale, int H, int N,
-                                                             long long total_rows) {
+__device__ __forceinline__ void pertoken_rows(const __half* __restrict__ x, long long sB, long long sH, long long sN,
+                                              int8_t* __restrict__ x8, float* __restrict__ scale, int H, int N,
+                                              long long total_rows, int cta, int ncta) {
   constexpr int LPR = D / 8;         // lanes per row
   constexpr int RPW = 32 / LPR;      // rows per warp and load
   const int lane = threadIdx.x & 31;
   const int sub = lane % LPR;
-  const long long warp_g = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  const long long warp_g = (long long)cta * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nwarps = (long long)ncta * (blockDim.x >> 5);
   for (long long row0 = warp_g * (RPW * kQuantUnroll); row0 < total_rows; row0 += nwarps * (RPW * kQuantUnroll)) {
     uint4 v[kQuantUnroll];
     long long rows[kQuantUnroll];
@@ -121,20 +122,29 @@ __global__ void __launch_bounds__(256) quant_pertoken_kernel(const __half* __res
   }
 }
 
-// column absmax of one (batch, head) slab chunk -> atomicMax into colmax[bh*D + ch]
-template <int D>
-__global__ void __launch_bounds__(256) v_colmax_kernel(const __half* __restrict__ x, long long sB, long long sH,
-                                                       long long sN, unsigned int* __restrict__ colmax, int H, int N,
-                                                       int rows_per_cta) {
+template <int D, bool CONTIG>
+__global__ void __launch_bounds__(256) quant_pertoken_kernel(const __half* __restrict__ x, long long sB, long long sH,
+                                                             long long sN, int8_t* __restrict__ x8,
+                                                             float* __restrict__ scale, int H, int N,
+                                                             long long total_rows) {
+  pertoken_rows<D, CONTIG>(x, sB, sH, sN, x8, scale, H, N, total_rows, blockIdx.x, gridDim.x);
+}
+
+// Column absmax of chunk `chunk` (rows_per_cta rows) of the (batch, head) slab `bh`.  ATOMIC: atomicMax on the bit
+// patterns of non-negative floats into colmax[bh*D + ch] (the caller has zeroed it); otherwise a plain store into
+// row `chunk` of a [chunks][B*H][D] array of partial maxima (nothing to clear, nothing to order).
+template <int D, bool ATOMIC>
+__device__ __forceinline__ void colmax_chunk(const __half* __restrict__ x, long long sB, long long sH, long long sN,
+                                             unsigned int* __restrict__ colmax, int H, int N, int rows_per_cta,
+                                             int chunk, int bh, int BH) {
   constexpr int LPR = D / 8;
   constexpr int RPW = 32 / LPR;
   __shared__ float red[8][D];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int sub = lane % LPR;
-  const int bh = blockIdx.y;
   const int b = bh / H, h = bh - b * H;
   const __half* base = x + b * sB + h * sH + sub * 8;
-  const int r_begin = blockIdx.x * rows_per_cta;
+  const int r_begin = chunk * rows_per_cta;
   const int r_end = min(N, r_begin + rows_per_cta);
   __half2 m[4];
 #pragma unroll
@@ -170,7 +180,36 @@ __global__ void __launch_bounds__(256) v_colmax_kernel(const __half* __restrict_
   for (int ch = threadIdx.x; ch < D; ch += blockDim.x) {
     float a = 0.f;
     for (int w = 0; w < nw; ++w) a = fmaxf(a, red[w][ch]);
-    atomicMax(colmax + (long long)bh * D + ch, __float_as_uint(a));
+    if (ATOMIC) atomicMax(colmax + (long long)bh * D + ch, __float_as_uint(a));
+    else colmax[((long long)chunk * BH + bh) * D + ch] = __float_as_uint(a);
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(256) v_colmax_kernel(const __half* __restrict__ x, long long sB, long long sH,
+                                                       long long sN, unsigned int* __restrict__ colmax, int H, int N,
+                                                       int rows_per_cta) {
+  colmax_chunk<D, true>(x, sB, sH, sN, colmax, H, N, rows_per_cta, blockIdx.x, blockIdx.y, gridDim.y);
+}
+
+// The first launch of the fused prologue: one grid over three jobs -- CTAs [0, gq) quantise the rows of Q,
+// [gq, gq+gk) those of K (both per token, contiguous tensors), the rest take one (chunk, batch*head) piece of V each and
+// store its column absmax as a partial result.  Nothing is shared between the jobs, so no ordering is needed.
+struct QkvJob {
+  const __half* q; int8_t* q8; float* qs; long long q_rows; int gq;
+  const __half* k; int8_t* k8; float* ks; long long k_rows; int gk;
+  const __half* v; long long vB, vH, vN; unsigned int* partial; int Hkv, Nk, rows_per_cta, chunks, BHkv;
+};
+template <int D>
+__global__ void __launch_bounds__(256) quant_qkv_kernel(const QkvJob j) {
+  const int cta = blockIdx.x;
+  if (cta < j.gq) {
+    pertoken_rows<D, true>(j.q, 0, 0, 0, j.q8, j.qs, 1, 1, j.q_rows, cta, j.gq);
+  } else if (cta < j.gq + j.gk) {
+    pertoken_rows<D, true>(j.k, 0, 0, 0, j.k8, j.ks, 1, 1, j.k_rows, cta - j.gq, j.gk);
+  } else {
+    const int i = cta - j.gq - j.gk;
+    colmax_chunk<D, false>(j.v, j.vB, j.vH, j.vN, j.partial, j.Hkv, j.Nk, j.rows_per_cta, i % j.chunks, i / j.chunks, j.BHkv);
   }
 }
 
@@ -178,7 +217,7 @@ template <int D>
 __global__ void __launch_bounds__(256) v_quant_kernel(const __half* __restrict__ x, long long sB, long long sH,
                                                       long long sN, const unsigned int* __restrict__ colmax,
                                                       int8_t* __restrict__ x8, float* __restrict__ scale,
-                                                      int per_channel, int H, int N, int rows_per_cta) {
+                                                      int per_channel, int H, int N, int rows_per_cta, int nparts) {
   constexpr int LPR = D / 8;
   constexpr int RPW = 32 / LPR;
   __shared__ float s_scale[D];
@@ -192,7 +231,8 @@ __global__ void __launch_bounds__(256) v_quant_kernel(const __half* __restrict__
     float all = 0.f;
 #pragma unroll
     for (int i = 0; i < D / 32; ++i) {
-      a[i] = __uint_as_float(colmax[(long long)bh * D + lane + 32 * i]);
+      a[i] = 0.f;      // colmax is [nparts][B*H][D]: one row, or the partial maxima of the fused first launch
+      for (int c = 0; c < nparts; ++c) a[i] = fmaxf(a[i], __uint_as_float(colmax[((long long)c * gridDim.y + bh) * D + lane + 32 * i]));
       all = fmaxf(all, a[i]);
     }
 #pragma unroll
@@ -291,20 +331,69 @@ int v_colmax(const void* v, const int64_t* st, void* colmax, int B, int H, int N
   return check_launch("v_colmax");
 }
 
-int v_quant_from_colmax(const void* v, const int64_t* st, const void* colmax, void* v8, float* scale, int mode, int B,
-                        int H, int N, int D, cudaStream_t stream) {
+static int v_quant_launch(const void* v, const int64_t* st, const void* colmax, int nparts, void* v8, float* scale, int mode,
+                          int B, int H, int N, int D, cudaStream_t stream) {
   const int sms = sm_count_cached();
   if (sms <= 0) return set_error(INTFA_ERR_CUDA, "cannot query SM count");
   int rows_per_cta;
   dim3 grid(v_grid(B * H, N, sms, &rows_per_cta), B * H);
   const int pc = mode == INTFA_VSCALE_PER_CHANNEL;
   if (D == 128)
-    v_quant_kernel<128><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (const unsigned int*)colmax, (int8_t*)v8, scale, pc, H, N, rows_per_cta);
+    v_quant_kernel<128><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (const unsigned int*)colmax, (int8_t*)v8, scale, pc, H, N, rows_per_cta, nparts);
   else if (D == 64)
-    v_quant_kernel<64><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (const unsigned int*)colmax, (int8_t*)v8, scale, pc, H, N, rows_per_cta);
+    v_quant_kernel<64><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (const unsigned int*)colmax, (int8_t*)v8, scale, pc, H, N, rows_per_cta, nparts);
   else
-    v_quant_kernel<32><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (const unsigned int*)colmax, (int8_t*)v8, scale, pc, H, N, rows_per_cta);
+    v_quant_kernel<32><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (const unsigned int*)colmax, (int8_t*)v8, scale, pc, H, N, rows_per_cta, nparts);
   return check_launch("v_quant");
+}
+
+int v_quant_from_colmax(const void* v, const int64_t* st, const void* colmax, void* v8, float* scale, int mode, int B,
+                        int H, int N, int D, cudaStream_t stream) {
+  return v_quant_launch(v, st, colmax, 1, v8, scale, mode, B, H, N, D, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// fused prologue: Q, K (per token) and V (per channel / per batch-head) in TWO launches, no memset
+// ---------------------------------------------------------------------------------------------
+size_t quant_qkv_workspace_bytes(int B, int Hkv, int Nk, int D) {
+  const int sms = sm_count_cached();
+  int rows_per_cta;
+  const int chunks = v_grid(B * Hkv, Nk, sms > 0 ? sms : 148, &rows_per_cta);
+  return (size_t)chunks * B * Hkv * D * sizeof(unsigned int);
+}
+
+int quant_qkv(const void* q, const void* k, const void* v, const int64_t* v_st, void* q8, void* k8, void* v8, float* qs,
+              float* ks, float* vs, int mode, int B, int H, int Hkv, int Nq, int Nk, int D, void* workspace,
+              cudaStream_t stream) {
+  const int sms = sm_count_cached();
+  if (sms <= 0) return set_error(INTFA_ERR_CUDA, "cannot query SM count");
+  QkvJob j;
+  j.q = (const __half*)q; j.q8 = (int8_t*)q8; j.qs = qs; j.q_rows = (long long)B * H * Nq;
+  j.k = (const __half*)k; j.k8 = (int8_t*)k8; j.ks = ks; j.k_rows = (long long)B * Hkv * Nk;
+  if (j.q_rows >= (1LL << 31) || j.k_rows >= (1LL << 31)) return set_error(INTFA_ERR_TOO_LARGE, "quant_qkv: B*H*N must be below 2^31");
+  const int rpw = 32 / (D / 8) * kQuantUnroll;
+  auto ctas = [&](long long rows) {
+    const long long want = (rows + 8LL * rpw - 1) / (8LL * rpw);
+    const long long cap = (long long)sms * 8;
+    return (int)(want < cap ? (want < 1 ? 1 : want) : cap);
+  };
+  j.gq = ctas(j.q_rows);
+  j.gk = ctas(j.k_rows);
+  j.v = (const __half*)v; j.partial = (unsigned int*)workspace; j.Hkv = Hkv; j.Nk = Nk; j.BHkv = B * Hkv;
+  j.chunks = 0; j.rows_per_cta = 0; j.vB = j.vH = j.vN = 0;
+  int gv = 0;
+  if (v) {
+    j.vB = v_st[0]; j.vH = v_st[1]; j.vN = v_st[2];
+    j.chunks = v_grid(B * Hkv, Nk, sms, &j.rows_per_cta);
+    gv = j.chunks * B * Hkv;
+  }
+  const int grid = j.gq + j.gk + gv;
+  if (D == 128) quant_qkv_kernel<128><<<grid, 256, 0, stream>>>(j);
+  else if (D == 64) quant_qkv_kernel<64><<<grid, 256, 0, stream>>>(j);
+  else quant_qkv_kernel<32><<<grid, 256, 0, stream>>>(j);
+  int rc = check_launch("quant_qkv");
+  if (rc || !v) return rc;
+  return v_quant_launch(v, v_st, workspace, j.chunks, v8, vs, mode, B, Hkv, Nk, D, stream);
 }
 
 int quant_v(const void* v, const int64_t* st, void* v8, float* scale, int mode, int B, int H, int N, int D,

@@ -261,6 +261,39 @@ def _quant_v(X, mode):
     return x8, scale
 
 
+def quant_qkv(q, k, v=None, v_mode="per_channel"):
+    """The quantisation prologue of one attention call in two launches (one when v is None): per-token q and k
+    (benchmark.py:96-100) and, in the same grid, the column absmax of v; then the v quantisation (benchmark.py:102-107
+    or its per-channel form).  Bit-identical to quant_pertoken / quant_perchannel / quant_pertensor called one by one.
+    Returns (q8, q_scale, k8, k_scale) and, with v, (v8, v_scale) appended."""
+    lib = _lib.load()
+    q, k = _quant_in(q).contiguous(), _quant_in(k).contiguous()
+    B, H, Nq, D = q.shape
+    Hkv, Nk = k.shape[1], k.shape[2]
+    q8 = torch.empty((B, H, Nq, D), dtype=torch.int8, device=q.device)
+    k8 = torch.empty((B, Hkv, Nk, D), dtype=torch.int8, device=q.device)
+    qs = torch.empty((B, H, Nq), dtype=torch.float32, device=q.device)
+    ks = torch.empty((B, Hkv, Nk), dtype=torch.float32, device=q.device)
+    v8 = vs = ws = None
+    mode = _lib.VSCALE_PER_CHANNEL if v_mode == "per_channel" else _lib.VSCALE_PER_TENSOR
+    vptr = v8ptr = vsptr = wsptr = None
+    vst = _lib._i64x3(0, 0, 0)
+    nbytes = 0
+    if v is not None:
+        v = _quant_in(v)
+        if v.shape != k.shape:
+            raise ValueError("k and v must have the same shape")
+        v8 = torch.empty((B, Hkv, Nk, D), dtype=torch.int8, device=q.device)
+        vs = torch.empty((B, Hkv, D) if mode == _lib.VSCALE_PER_CHANNEL else (B, Hkv), dtype=torch.float32, device=q.device)
+        nbytes = lib.intfa_quant_qkv_workspace_bytes(B, Hkv, Nk, D)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+        vptr, v8ptr, vsptr, wsptr, vst = v.data_ptr(), v8.data_ptr(), vs.data_ptr(), ws.data_ptr(), _lib._i64x3(*v.stride()[:3])
+    with torch.cuda.device(q.device):
+        _lib.check(lib.intfa_quant_qkv(q.data_ptr(), k.data_ptr(), vptr, vst, q8.data_ptr(), k8.data_ptr(), v8ptr,
+                                       qs.data_ptr(), ks.data_ptr(), vsptr, mode, B, H, Hkv, Nq, Nk, D, wsptr, nbytes, _stream(q)))
+    return (q8, qs, k8, ks) if v is None else (q8, qs, k8, ks, v8, vs)
+
+
 def quant_v_with_allreduce(X, mode, group=None):
     """V quantisation for a token-sharded V: local column absmax, all-reduce(MAX) over `group`
     of the B*H*D fp32 bit patterns (order-preserving as int32 because they are non-negative),
@@ -299,9 +332,8 @@ def int_flash_attention(q, k, v, causal, sm_scale, variant="full", v_mode="per_c
     """fp16 Q/K/V in, fp16 O out: fused quantisation prologue (per-token Q/K; per-channel or
     per-(batch,head) V for the full-int8 variant) followed by the INT8 attention forward.
     Argument order follows the reference's attention(q, k, v, causal, sm_scale) (flash_atten_fp.py:155)."""
-    q8, qs = quant_pertoken(q)
-    k8, ks = quant_pertoken(k)
     if variant == "full":
-        v8, vs = quant_perchannel(v) if v_mode == "per_channel" else quant_pertensor(v)
+        q8, qs, k8, ks, v8, vs = quant_qkv(q, k, v, v_mode)
         return attention_full_int8(q8, k8, v8, qs, ks, vs, causal, sm_scale, **kw)
+    q8, qs, k8, ks = quant_qkv(q, k)
     return attention_int8(q8, k8, v, qs, ks, causal, sm_scale, **kw)

@@ -21,6 +21,30 @@ def _modules():
 def test_dropin_modules_export_the_reference_names():
     half, full = _modules()
     assert callable(half.attention_int8) and callable(full.attention_full_int8)
+    # the other two modules benchmark.py imports (benchmark.py:9,11) resolve inside the drop-in directory as well
+    fp, cfg = importlib.import_module("flash_atten_fp"), importlib.import_module("configs")
+    assert os.path.dirname(os.path.abspath(fp.__file__)) == os.path.abspath(DROPIN)
+    assert os.path.dirname(os.path.abspath(cfg.__file__)) == os.path.abspath(DROPIN)
+    assert callable(fp.attention) and cfg.is_hip() is False and isinstance(cfg.configs, list) and cfg.keep(None)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("causal", [False, True])
+def test_float_baseline_pass_through(causal):
+    """`attention(q, k, v, causal, sm_scale)` as benchmark.py:156,167 call it: fp16, then fp8 (e5m2) inputs."""
+    _modules()
+    fp = importlib.import_module("flash_atten_fp")
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(21)
+    q, k, v = (torch.rand(1, 2, 128, 64, generator=g).half().to(dev) for _ in range(3))
+    s = torch.matmul(q.float(), k.float().transpose(2, 3)) * 0.7
+    if causal:
+        s = s + torch.triu(torch.full((128, 128), float("-inf"), device=dev), 1)
+    ref = torch.matmul(torch.softmax(s, dim=-1), v.float())
+    out = fp.attention(q, k, v, causal, 0.7)
+    assert out.dtype == torch.float16 and (out.float() - ref).abs().max() < 1e-2          # benchmark.py:242
+    out8 = fp.attention(q.to(torch.float8_e5m2), k.to(torch.float8_e5m2), v.to(torch.float8_e5m2), causal, 0.7)
+    assert out8.dtype == torch.float8_e5m2 and (out8.float() - ref).abs().max() < 0.2
 
 
 @pytest.mark.gpu

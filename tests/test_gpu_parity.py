@@ -615,3 +615,27 @@ def test_a_wait_that_runs_out_is_reported_and_the_next_call_works(pkg, oracle, d
     out = pkg.attention_full_int8(*args)
     assert pkg.check_status() == 0
     _close(oracle, out, oracle.attention_full_int8(q8, k8, v8, qs, ks, vs, False, 0.09))
+
+
+@pytest.mark.parametrize("B,H,Hkv,Nq,Nk,D,mode", [(2, 4, 4, 512, 512, 128, "per_channel"), (1, 4, 2, 256, 1000, 64, "per_tensor"),
+                                                  (1, 2, 2, 8, 40, 32, "per_channel"), (4, 32, 32, 2048, 2048, 128, "per_channel")])
+def test_fused_prologue_bit_exact(B, H, Hkv, Nq, Nk, D, mode, pkg, oracle, dev):
+    """quant_qkv (two launches, no memset) against the oracle's quantisers and against the one-by-one entry points."""
+    q, _, _ = make_qkv(71, B, H, Nq, D)
+    _, k, v = make_qkv(72, B, Hkv, Nk, D)
+    k[0, 0, 3] = 0
+    v[..., 5] = 0                                    # an all-zero token and an all-zero channel
+    q8, qs, k8, ks, v8, vs = pkg.quant_qkv(q.to(dev), k.to(dev), v.to(dev), mode)
+    small = B * H * Nq * D <= 1 << 22
+    if small:
+        rq8, rqs = oracle.zero_safe(*oracle.quant_pertoken(q), q, 3)
+        rk8, rks = oracle.zero_safe(*oracle.quant_pertoken(k), k, 3)
+        assert torch.equal(q8.cpu(), rq8) and torch.equal(qs.cpu(), rqs.float())
+        assert torch.equal(k8.cpu(), rk8) and torch.equal(ks.cpu(), rks.float())
+    a8, a_s = pkg.quant_pertoken(q.to(dev))
+    b8, b_s = pkg.quant_pertoken(k.to(dev))
+    c8, c_s = (pkg.quant_perchannel if mode == "per_channel" else pkg.quant_pertensor)(v.to(dev))
+    for x, y in ((q8, a8), (qs, a_s), (k8, b8), (ks, b_s), (v8, c8), (vs, c_s)):
+        assert torch.equal(x, y)
+    h8, hs, g8, gs = pkg.quant_qkv(q.to(dev), k.to(dev))        # half-int8: no V
+    assert torch.equal(h8, a8) and torch.equal(gs, b_s)
