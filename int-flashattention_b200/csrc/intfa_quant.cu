@@ -59,16 +59,29 @@ __device__ __forceinline__ uint2 quant8(const uint4& v, const float* s, const fl
   return make_uint2(w[0], w[1]);
 }
 
-// streaming 128-bit load / 64-bit store: the tensors are touched once, keep them out of L1
-__device__ __forceinline__ uint4 ld_stream(const void* p) {
+// L2 residency hints.  The first launch of the fused prologue reads V for its column maxima and the second reads it
+// again to quantise it: V is loaded "evict last" there and everything that is touched once (Q, K, every int8 store)
+// "evict first", and the second launch walks the (batch, head) slabs in the opposite order, so that the slabs read
+// last -- as much of V as the L2 holds -- are served from L2 instead of HBM.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint4 ld_hint(const void* p, uint64_t policy) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
+               : "l"(p), "l"(policy));
   return v;
 }
-__device__ __forceinline__ void st_stream(void* p, uint2 v) {
-  asm volatile("st.global.cs.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+__device__ __forceinline__ void st_hint(void* p, uint2 v, uint64_t policy) {
+  asm volatile("st.global.L2::cache_hint.v2.u32 [%0], {%1, %2}, %3;" ::"l"(p), "r"(v.x), "r"(v.y), "l"(policy) : "memory");
 }
 
 constexpr int kQuantUnroll = 4;    // independent 128-bit loads in flight per lane
@@ -84,6 +97,7 @@ __device__ __forceinline__ void pertoken_rows(const __half* __restrict__ x, long
   const int sub = lane % LPR;
   const long long warp_g = (long long)cta * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long nwarps = (long long)ncta * (blockDim.x >> 5);
+  const uint64_t once = l2_policy_evict_first();
   for (long long row0 = warp_g * (RPW * kQuantUnroll); row0 < total_rows; row0 += nwarps * (RPW * kQuantUnroll)) {
     uint4 v[kQuantUnroll];
     long long rows[kQuantUnroll];
@@ -94,14 +108,14 @@ __device__ __forceinline__ void pertoken_rows(const __half* __restrict__ x, long
       v[u] = make_uint4(0, 0, 0, 0);
       if (row < total_rows) {
         if (CONTIG) {
-          v[u] = ld_stream(x + row * D + sub * 8);          // [B,H,N,D] contiguous: the row index is the address
+          v[u] = ld_hint(x + row * D + sub * 8, once);      // [B,H,N,D] contiguous: the row index is the address
         } else {
           // total_rows < 2^31 (checked by the host): 32-bit divisions
           const unsigned int r32 = (unsigned int)row;
           const unsigned int bh = r32 / (unsigned int)N;
           const unsigned int n = r32 - bh * (unsigned int)N;
           const unsigned int b = bh / (unsigned int)H, h = bh - b * (unsigned int)H;
-          v[u] = ld_stream(x + (long long)b * sB + (long long)h * sH + (long long)n * sN + sub * 8);
+          v[u] = ld_hint(x + (long long)b * sB + (long long)h * sH + (long long)n * sN + sub * 8, once);
         }
       }
     }
@@ -115,7 +129,7 @@ __device__ __forceinline__ void pertoken_rows(const __half* __restrict__ x, long
         const float rcp = __frcp_rn(s);
         const float sv[8] = {s, s, s, s, s, s, s, s};
         const float rv[8] = {rcp, rcp, rcp, rcp, rcp, rcp, rcp, rcp};
-        st_stream(x8 + rows[u] * D + sub * 8, quant8(v[u], sv, rv));
+        st_hint(x8 + rows[u] * D + sub * 8, quant8(v[u], sv, rv), once);
         if (sub == 0) scale[rows[u]] = s;
       }
     }
@@ -146,6 +160,7 @@ __device__ __forceinline__ void colmax_chunk(const __half* __restrict__ x, long 
   const __half* base = x + b * sB + h * sH + sub * 8;
   const int r_begin = chunk * rows_per_cta;
   const int r_end = min(N, r_begin + rows_per_cta);
+  const uint64_t keep = l2_policy_evict_last();
   __half2 m[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) m[i] = __float2half2_rn(0.f);
@@ -154,7 +169,7 @@ __device__ __forceinline__ void colmax_chunk(const __half* __restrict__ x, long 
 #pragma unroll
     for (int u = 0; u < kQuantUnroll; ++u) {
       const int r = r0 + u * nw * RPW;
-      v[u] = r < r_end ? *reinterpret_cast<const uint4*>(base + r * sN) : make_uint4(0, 0, 0, 0);
+      v[u] = r < r_end ? ld_hint(base + r * sN, keep) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int u = 0; u < kQuantUnroll; ++u) {
@@ -223,8 +238,9 @@ __global__ void __launch_bounds__(256) v_quant_kernel(const __half* __restrict__
   __shared__ float s_scale[D];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int sub = lane % LPR;
-  const int bh = blockIdx.y;
+  const int bh = gridDim.y - 1 - blockIdx.y;     // last slab first: the column-absmax pass read it last
   const int b = bh / H, h = bh - b * H;
+  const uint64_t once = l2_policy_evict_first();
   if (threadIdx.x < 32) {
     // every channel's absmax; for the per-(batch,head) mode reduce them to one
     float a[D / 32];
@@ -263,12 +279,12 @@ __global__ void __launch_bounds__(256) v_quant_kernel(const __half* __restrict__
 #pragma unroll
     for (int u = 0; u < kQuantUnroll; ++u) {
       const int r = r0 + u * nw * RPW;
-      v[u] = r < r_end ? ld_stream(base + r * sN) : make_uint4(0, 0, 0, 0);
+      v[u] = r < r_end ? ld_hint(base + r * sN, once) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int u = 0; u < kQuantUnroll; ++u) {
       const int r = r0 + u * nw * RPW;
-      if (r < r_end) st_stream(obase + (long long)r * D, quant8(v[u], sv, rv));
+      if (r < r_end) st_hint(obase + (long long)r * D, quant8(v[u], sv, rv), once);
     }
   }
 }
