@@ -353,7 +353,8 @@ def run_ring(args, pkg, dist, rank, world, local_rank, dev):
             print(json.dumps({"metric": METRIC, "unavailable": "the ring workload needs --gpus >= 2"}), flush=True)
         return
     steps = min(args.steps, 10)
-    ms, clocks, nh = measure_ring(pkg, dist, rank, world, local_rank, dev, args.workload, steps, args.warmup)
+    ms, clocks, nh = measure_ring(pkg, dist, rank, world, local_rank, dev, args.workload, steps, args.warmup,
+                                  prefetch=args.ring_prefetch or None)
     check = ring_self_check(pkg, dist, rank, world, local_rank, dev)
     ops = attn_ops(B, H, N, D, True)
     if rank == 0:
@@ -367,6 +368,7 @@ def run_ring(args, pkg, dist, rank, world, local_rank, dev):
                 "config": {"workload": args.workload, "variant": variant, "B": B, "H": H, "N_global": N, "D": D,
                            "causal": True, "layout": "zigzag half-chunks, ascending ring, NCCL send/recv",
                            "half_chunk_rows": nh, "bytes_per_half_chunk_transfer": kv_bytes,
+                           "prefetch": args.ring_prefetch or "all transfers posted up front",
                            "l2": "inputs exceed L2"},
                 "clocks": clocks, "gpu_launches": steps * (5 + 2 * world + 1), "ring_check": check,
                 "roofline": {"bound": "tensor", "kernel": "intfa_fwd_pipe_kernel", "achieved": value / world,
@@ -385,6 +387,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + ["int8_peak"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--ring-prefetch", type=int, default=0, help="ring workload: half-chunk transfers posted ahead of the attention launches (0 = all up front)")
     ap.add_argument("--no-multi", action="store_true", help="with --gpus >= 2: skip the ring and strong-scaling sub-measurements")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

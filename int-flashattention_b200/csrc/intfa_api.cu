@@ -109,9 +109,7 @@ int intfa_fwd(const IntfaFwdParams* p, void* stream) {
   if ((p->state_in || p->state_out) && !aligned16(p->state_acc))
     return set_error(INTFA_ERR_INVALID_ARG, "state_acc must be 16-byte aligned");
   if (!p->write_o && !p->state_out) return set_error(INTFA_ERR_INVALID_ARG, "nothing to write: write_o and state_out are both 0");
-  #if !defined(INTFA_TIMING) && !defined(INTFA_TRACE)
   if (p->dbg_s && (p->dbg_tile < 0 || p->dbg_step < 0)) return set_error(INTFA_ERR_INVALID_ARG, "bad debug tap");
-#endif
   return fwd_dispatch(p, reinterpret_cast<cudaStream_t>(stream));
 }
 

@@ -91,40 +91,6 @@ __device__ __forceinline__ uint32_t swz_off(int row, int chunk) {
   return a ^ (((a >> 7) & MASK) << 4);
 }
 
-#ifdef INTFA_TRACE
-// event trace of 16 consecutive KV steps of CTA 0: dbg_s[((role*16 + step)*8 + event)] = low bits of clock64
-#define INTFA_TR(role, step, ev)                                                                              \
-  if (p.dbg_s != nullptr && p.dbg_tile == -3 && blockIdx.x == 0 && lane == 0 && (int)(step) >= p.dbg_step &&   \
-      (int)(step) < p.dbg_step + 16)                                                                           \
-    p.dbg_s[(((role) * 16 + ((int)(step) - p.dbg_step)) * 8 + (ev))] = (int)(clock64() & 0x7fffffff);
-#else
-#define INTFA_TR(role, step, ev)
-#endif
-#ifdef INTFA_TIMING
-#define INTFA_T0() tq = clock64()
-#define INTFA_T(i) { const long long now_ = clock64(); tm[i] += now_ - tq; tq = now_; }
-#define INTFA_TDECL() long long tm[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tq = 0
-#define INTFA_TDUMP_SOFTMAX()                                                                        \
-  if (lane == 0 && p.dbg_s != nullptr && p.dbg_tile == -2 && blockIdx.x < 400 && grp == 0) {         \
-    for (int i = 0; i < 6; ++i) p.dbg_s[(blockIdx.x * 4 + quarter) * 8 + i] = (int)(tm[i] >> 4);     \
-  }
-#define INTFA_TDUMP_MMA()                                                                            \
-  if (lane == 0 && p.dbg_s != nullptr && p.dbg_tile == -2 && blockIdx.x < 400) {                     \
-    for (int i = 0; i < 8; ++i) if (tm[i]) p.dbg_s[12800 + blockIdx.x * 8 + i] = (int)(tm[i] >> 4);  \
-  }
-#define INTFA_TDUMP_UPDATE()                                                                         \
-  if (lane == 0 && p.dbg_s != nullptr && p.dbg_tile == -2 && blockIdx.x < 400) {                     \
-    for (int i = 6; i < 8; ++i) p.dbg_s[(blockIdx.x * 4 + quarter) * 8 + i] = (int)(tm[i] >> 4);     \
-  }
-#else
-#define INTFA_T0()
-#define INTFA_T(i)
-#define INTFA_TDECL()
-#define INTFA_TDUMP_SOFTMAX()
-#define INTFA_TDUMP_MMA()
-#define INTFA_TDUMP_UPDATE()
-#endif
-
 #include "intfa_fwd_pipe.cuh"
 
 // ============================================================================

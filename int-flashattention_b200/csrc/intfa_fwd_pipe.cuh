@@ -238,7 +238,6 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tma_load_4d(sK + s * C::K_BYTES, &tmK, BAR(B_KFULL + s), 0, jb * G, t.hk, t.b);
             bulk_load_1d(sKS + (kv_it % C::NKS) * C::KS_BYTES, ks_row + jb * G, C::KS_BYTES, BAR(B_KFULL + s));
           }
-          INTFA_TR(5, kv_it, 0);
           const uint32_t sv = kv_it % NSV, phv = (kv_it / NSV) & 1;
           ok = mbar_wait(BAR(B_VEMPTY + sv), phv ^ 1, abort_flag, p.status, code_hi | PW_VE);
           if (!ok) break;
@@ -250,7 +249,6 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             for (int c = 0; c < C::V_BOXES; ++c)
               tma_load_4d(sV + sv * C::V_BYTES + c * (G * 128), &tmV, BAR(B_VFULL + sv), c * 64, jb * G, t.hk, t.b);
           }
-          INTFA_TR(5, kv_it, 1);
         }
         ++tile_it;
       }
@@ -266,7 +264,6 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       // K scales sit in a ring of their own).
       uint32_t kv_it = 0, tile_it = 0, tseq = 0, sfree_seen = 0;
       bool ok = true;
-      INTFA_TDECL();
       // operand descriptors of stage 0 / K step 0; the start-address field (16-byte units) takes the offsets
       const uint64_t descQ0 = make_smem_desc(sQ, 16, C::SBO_QK, C::SWZ_QK);
       const uint64_t descK0 = make_smem_desc(sK, 16, C::SBO_QK, C::SWZ_QK);
@@ -275,26 +272,20 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (tile < 0) break;
         const TileInfo t = decode_tile<RAGGED>(p, tile, G);
         if (t.nsteps == 0) continue;
-        INTFA_T0();
         ok = mbar_wait_warp(BAR(B_QFULL), tile_it & 1, abort_flag, p.status, code_hi | PW_QF);
         if (!ok) break;
-        INTFA_T(0);
         for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
           const uint32_t s = kv_it % NSK, ph = (kv_it / NSK) & 1;
           const uint32_t sb = kv_it % NSB;
-          INTFA_T0();
           // every S_FREE is waited for exactly once, in step order, so the phases of the barriers stay in step
           while (ok && sfree_seen + NSB <= kv_it) {
             ok = mbar_wait_warp(BAR(B_SFREE + sfree_seen % NSB), (sfree_seen / NSB) & 1, abort_flag, p.status, code_hi | PW_SFREE);
             ++sfree_seen;
           }
           if (!ok) break;
-          INTFA_T(7);
-          INTFA_TR(2, kv_it, 0);
           ok = mbar_wait_warp(BAR(B_KFULL + s), ph, abort_flag, p.status, code_hi | PW_KF);
           if (!ok) break;
           tc_fence_after();
-          INTFA_T(1);
           const uint64_t bd0 = descK0 + (uint64_t)(s * (C::K_BYTES >> 4));
           const uint32_t tSb = tS + sb * G;
           if (elect_one()) {
@@ -306,12 +297,9 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             if (j + 1 == t.nsteps) umma_commit(BAR(B_QEMPTY));
           }
           __syncwarp();
-          INTFA_T(2);
-          INTFA_TR(2, kv_it, 1);
         }
         ++tile_it;
       }
-      INTFA_TDUMP_MMA();
     }
     __syncwarp();
   } else if (warp == 3) {
@@ -321,7 +309,6 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       // Per step j: [P(j) written] [V(j) landed] [O_j of step j-1 read out] PV(j).
       uint32_t kv_it = 0, tseq = 0;
       bool ok = true;
-      INTFA_TDECL();
       const uint64_t descP0 = make_smem_desc(sP, 16, C::SBO_P, C::SWZ_P);
       const uint64_t descV0 = make_smem_desc(sV, FULL ? 16 : G * 128, C::SBO_V, C::SWZ_V);
       while (ok) {
@@ -334,20 +321,15 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           // P(j) written; V(j) landed; full-int8: O_j of the previous step has been read out, half-int8: the
           // accumulator has been brought to this step's running max (and the previous P V has landed in it).
           // (One copy of the wait code for the three.)
-          INTFA_T0();
 #pragma unroll 1
           for (int w = 0; w < 3; ++w) {
             const uint32_t wb = w == 0 ? BAR(B_PFULL + b) : w == 1 ? BAR(B_VFULL + s) : BAR(B_OFREE);
             const uint32_t wp = w == 0 ? ((kv_it >> 1) & 1) : w == 1 ? ph : (FULL ? ((kv_it & 1) ^ 1) : (kv_it & 1));
             ok = mbar_wait_warp(wb, wp, abort_flag, p.status, code_hi | (w == 0 ? PW_PFULL : w == 1 ? PW_VF : PW_OFREE));
             if (!ok) break;
-            if (w == 0) { INTFA_TR(2, kv_it, 2); }
-            if (w == 1) { INTFA_TR(2, kv_it, 3); }
           }
           if (!ok) break;
           tc_fence_after();
-          INTFA_T(5);
-          INTFA_TR(2, kv_it, 4);
           const uint64_t ad0 = descP0 + (uint64_t)(b * (C::P_BYTES >> 4));
           const uint64_t vd0 = descV0 + (uint64_t)(s * (C::V_BYTES >> 4));
           if (elect_one()) {
@@ -369,23 +351,10 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             umma_commit(BAR(B_PFREE + b));
           }
           __syncwarp();
-          INTFA_T(6);
-          INTFA_TR(2, kv_it, 5);
         }
       }
-      INTFA_TDUMP_MMA();
     }
     __syncwarp();
-#ifdef INTFA_TRACE
-  } else if (warp == 2) {
-    // trace builds: timestamps of the completion of S = Q K^T of every step (role 4)
-    if (p.dbg_s != nullptr && p.dbg_tile == -3 && blockIdx.x == 0) {
-      for (uint32_t it = 0; it < (uint32_t)(p.dbg_step + 16); ++it) {
-        if (!mbar_wait_warp(BAR(B_SFULL + it % NSB), (it / NSB) & 1, abort_flag, p.status, code_hi | PW_SFULL)) break;
-        INTFA_TR(4, it, 0);
-      }
-    }
-#endif
   } else if (warp >= 4 && warp < 12) {
     reg_alloc<kPipeSoftmaxRegs>();
 #include "intfa_fwd_pipe_softmax.inc"

@@ -104,4 +104,6 @@ def main(ref_dir):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <path to the reference checkout>")
+    main(sys.argv[1])

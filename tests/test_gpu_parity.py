@@ -109,7 +109,7 @@ def test_qk_tile_and_p_tile(D, G, variant, pkg, oracle, dev):
 # ------------------------------------------------------------------------------- attention vs oracle
 CASES = [
     # B, H, N, D, G, causal
-    (1, 4, 512, 64, 64, False),          # BASELINE config 0
+    (1, 4, 512, 64, 64, False),          # the CPU-runnable plumbing case: batch 1, heads 4, seq 512, head_dim 64
     (1, 2, 128, 128, 128, False),        # one tile
     (2, 3, 384, 128, 128, False),
     (1, 2, 512, 128, 64, False),
@@ -398,14 +398,14 @@ def test_unsupported_shapes_raise(pkg, dev):
 
 
 # ------------------------------------------------------------------------------- full-size workloads
-def _full_size(pkg, oracle, dev, B, H, N, D, variant, causal, seed, outlier, heads):
+def _full_size(pkg, oracle, dev, B, H, N, D, variant, causal, seed, outlier, heads, std=1.0):
     """Run the whole configuration on the GPU from fp16 inputs; check sampled (batch, head) slices
     against the CPU oracle, that a second run is bit-identical (no pipeline race), and that permuting
     the batch permutes the output (work items are independent)."""
     gen = torch.Generator(device=dev).manual_seed(seed)
-    q = torch.randn(B, H, N, D, device=dev, generator=gen, dtype=torch.float32).half()
-    k = torch.randn(B, H, N, D, device=dev, generator=gen, dtype=torch.float32).half()
-    v = torch.randn(B, H, N, D, device=dev, generator=gen, dtype=torch.float32).half()
+    q = (std * torch.randn(B, H, N, D, device=dev, generator=gen, dtype=torch.float32)).half()
+    k = (std * torch.randn(B, H, N, D, device=dev, generator=gen, dtype=torch.float32)).half()
+    v = (std * torch.randn(B, H, N, D, device=dev, generator=gen, dtype=torch.float32)).half()
     if outlier:
         q[..., 17] *= 20
         k[..., 17] *= 20
@@ -428,13 +428,24 @@ def _full_size(pkg, oracle, dev, B, H, N, D, variant, causal, seed, outlier, hea
 
 
 def test_full_size_full_int8_noncausal(pkg, oracle, dev):
-    """BASELINE config 1: batch 4, heads 32, seq 8192, head_dim 128, non-causal."""
+    """The headline workload at full size: batch 4, heads 32, seq 8192, head_dim 128, non-causal."""
     _full_size(pkg, oracle, dev, 4, 32, 8192, 128, "full", False, 1001, False, [(0, 0), (3, 31)])
 
 
 def test_full_size_half_int8_causal(pkg, oracle, dev):
-    """BASELINE config 2: batch 8, heads 32, seq 4096, head_dim 128, causal, outlier channel."""
+    """The half-int8 workload at full size: batch 8, heads 32, seq 4096, head_dim 128, causal, outlier channel."""
     _full_size(pkg, oracle, dev, 8, 32, 4096, 128, "half", True, 1002, True, [(0, 0), (7, 13)])
+
+
+def test_shard_shape_of_the_strong_scaling_workload(pkg, oracle, dev):
+    """One rank's share of batch 64 x heads 64 x seq 4096 over 8 GPUs: batch 8, heads 64, seq 4096, head_dim 128."""
+    _full_size(pkg, oracle, dev, 8, 64, 4096, 128, "full", False, 1003, False, [(0, 0), (7, 63)])
+
+
+def test_long_causal_rows(pkg, oracle, dev):
+    """Full-int8 causal at seq 16384 (std 0.5): the last query blocks walk 128 KV steps -- the longest runs of the
+    magic-number accumulators, the barrier phases and the S-buffer / stage rings between two work items."""
+    _full_size(pkg, oracle, dev, 1, 2, 16384, 128, "full", True, 1004, False, [(0, 1)], std=0.5)
 
 
 # --------------------------------------------------- the CUDA path's surface: grouped heads, bf16 output
