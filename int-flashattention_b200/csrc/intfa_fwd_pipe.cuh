@@ -50,9 +50,9 @@ struct PipeCfg {
   static constexpr int OFF_KS = OFF_P + 2 * P_BYTES;
   static constexpr int OFF_VSD = OFF_KS + NKS * KS_BYTES;         // s_v/127 per channel
   static constexpr int OFF_HM = OFF_VSD + D * 4;                  // [2 groups][128] float: running max after the group's latest step
-  static constexpr int OFF_HL = OFF_HM + 2 * 128 * 4;             // [2 groups][128] float: row sum after the group's latest step
-  static constexpr int OFF_ALPHA = OFF_HL + 2 * 128 * 4;          // [4][128] float: alpha of step j for the updater
-  static constexpr int OFF_FIN = OFF_ALPHA + 4 * 128 * 4;         // [2][128] float2: final (m, l) of a work item
+  static constexpr int OFF_RS = OFF_HM + 2 * 128 * 4;             // [4][128] float: row sum of P of step j, for the accumulator warps
+  static constexpr int OFF_ALPHA = OFF_RS + 4 * 128 * 4;          // [4][128] float: alpha of step j, for the accumulator warps
+  static constexpr int OFF_FIN = OFF_ALPHA + 4 * 128 * 4;         // [2][128] float2: final running max of a work item (.x)
   static constexpr int OFF_MAGIC = OFF_FIN + 2 * 128 * 8;          // 4 KB constant fp16 operand of the "arm" MMA
   static constexpr int MAGIC_BYTES = 4096;
   static constexpr int OFF_BAR = OFF_MAGIC + MAGIC_BYTES;
@@ -111,7 +111,6 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                                   //     before a slow accumulator warp has waited for the first completion
   constexpr int B_FINFREE = 12;   // [2] updater (8 warps): it has read them
   constexpr int B_HM = 14;        // [2] softmax group g (4 warps): running max after its step published
-  constexpr int B_HL = 16;        // [2] softmax group g (4 warps): row sum after its step published
   constexpr int B_KFULL = 18, B_KEMPTY = 18 + NSK, B_VFULL = 18 + 2 * NSK, B_VEMPTY = 18 + 2 * NSK + NSV;
   constexpr int B_TILE = 18 + 2 * NSK + 2 * NSV, B_TDONE = B_TILE + 4;
   constexpr int B_AFULL = B_TDONE + 4;   // [4] half-int8: alpha of step j (slot j mod 4) published, for the accumulator warps
@@ -129,7 +128,6 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       mbar_init(BAR(B_PFREE + b), 1);
       mbar_init(BAR(B_FINFREE + b), 4);
       mbar_init(BAR(B_HM + b), 4);
-      mbar_init(BAR(B_HL + b), 4);
       mbar_init(BAR(B_FIN + b), 4);
     }
     mbar_init(BAR(B_OFULL), 1);
