@@ -43,6 +43,11 @@ struct PipeCfg {
   static constexpr int NKS = 8;                                    // K-scale slots: a slot is rewritten 8 steps later, when
                                                                    // the three S buffers have long forced its step out
   static constexpr int NSB = 3;                                    // S buffers in TMEM
+  // Who carries the row sum l = l*alpha + rowsum(P)?  Where a KV step is as wide as the head (G >= D) the accumulator
+  // warps do, next to the accumulator row: the softmax groups then meet once per step (running max) instead of
+  // twice.  Where the head is wider than the step (head_dim 128 at G = 64) the accumulator warps are the busier
+  // side and the softmax groups keep l, handing it over like the running max (measured: 582 against 474 TOPS).
+  static constexpr bool L_IN_ACC = G >= D;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
   static constexpr int OFF_V = OFF_K + NSK * K_BYTES;
@@ -51,6 +56,7 @@ struct PipeCfg {
   static constexpr int OFF_VSD = OFF_KS + NKS * KS_BYTES;         // s_v/127 per channel
   static constexpr int OFF_HM = OFF_VSD + D * 4;                  // [2 groups][128] float: running max after the group's latest step
   static constexpr int OFF_RS = OFF_HM + 2 * 128 * 4;             // [4][128] float: row sum of P of step j, for the accumulator warps
+                                                                   //   (!L_IN_ACC: [2 groups][128] float, l after the group's latest step)
   static constexpr int OFF_ALPHA = OFF_RS + 4 * 128 * 4;          // [4][128] float: alpha of step j, for the accumulator warps
   static constexpr int OFF_FIN = OFF_ALPHA + 4 * 128 * 4;         // [2][128] float2: final running max of a work item (.x)
   static constexpr int OFF_MAGIC = OFF_FIN + 2 * 128 * 8;          // 4 KB constant fp16 operand of the "arm" MMA
@@ -106,6 +112,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   constexpr int B_PFREE = 6;      // [2] commit: the P V that read P buffer b is done
   constexpr int B_OFULL = 8;      // commit: O_j = P V in TMEM
   constexpr int B_OFREE = 9;      // updater (8 warps): O_j read out
+  constexpr int B_HL = 16;        // [2] !L_IN_ACC: softmax group g (4 warps): row sum after its step published
   constexpr int B_FIN = 10;       // [2] softmax (4 warps of one group): final (m, l) of the work item published; one
                                   //     barrier per slot, so that a short next work item cannot complete it twice
                                   //     before a slow accumulator warp has waited for the first completion
@@ -128,6 +135,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       mbar_init(BAR(B_PFREE + b), 1);
       mbar_init(BAR(B_FINFREE + b), 4);
       mbar_init(BAR(B_HM + b), 4);
+      mbar_init(BAR(B_HL + b), 4);
       mbar_init(BAR(B_FIN + b), 4);
     }
     mbar_init(BAR(B_OFULL), 1);
