@@ -61,7 +61,7 @@ typedef struct IntfaFwdParams {
   const float* q_scale;  const float* k_scale;  const float* v_scale;
   int64_t q_stride[3];  int64_t k_stride[3];  int64_t v_stride[3];  int64_t o_stride[3];
   int64_t qs_stride[2]; int64_t ks_stride[2]; int64_t vs_stride[3];
-  int32_t B, H, Nq, Nk, D;      /* D in {32,64,128}.  Nq, Nk need not be multiples of the tile sizes (128 rows, G
+  int32_t B, H, Nq, Nk, D;      /* D in {16,32,64,128,256} (flash_atten_full_int8.py:193).  Nq, Nk need not be multiples of the tile sizes (128 rows, G
                                    columns): the last tiles are masked (csrc/mask.h:277-285); but every row of
                                    k_scale must be ALLOCATED up to the next multiple of G floats (the values past
                                    Nk are ignored) -- the scales of a KV step are fetched G at a time */
@@ -69,7 +69,7 @@ typedef struct IntfaFwdParams {
   int32_t causal;               /* 0/1; mask is (kv_offset + col) <= (q_offset + row) */
   float   sm_scale;             /* natural-log softmax scale; kernel multiplies by 1.44269504 */
   int32_t G;                    /* running-max column granularity = KV tile width: 64 or 128 (32 as well for
-                                   full-int8 at D=32)
+                                   full-int8 at D<=32; half-int8 at D=256: 64 only)
                                    (the reference's BLOCK_N; full-int8 results depend on it).  The
                                    reference only allows BLOCK_N <= HEAD_DIM (flash_atten_full_int8.py:88);
                                    G=128 with D=64 is accepted here as a faster granularity of its own. */

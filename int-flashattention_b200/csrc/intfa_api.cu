@@ -50,6 +50,9 @@ static int check_tma_tensor(const char* name, const void* ptr, const int64_t* st
 
 using namespace intfa;
 
+// the head dims of the reference's ops (flash_atten_full_int8.py:193)
+static bool head_dim_ok(int D) { return D == 16 || D == 32 || D == 64 || D == 128 || D == 256; }
+
 extern "C" {
 
 int intfa_version(void) { return 100; }
@@ -70,16 +73,18 @@ int intfa_fwd(const IntfaFwdParams* p, void* stream) {
   const bool full = p->variant == INTFA_VARIANT_FULL;
   if (p->B <= 0 || p->H <= 0 || p->Nq <= 0 || p->Nk <= 0)
     return set_error(INTFA_ERR_INVALID_ARG, "B, H, Nq, Nk must be positive");
-  if (p->D != 32 && p->D != 64 && p->D != 128)
-    return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: the sm_100a kernels cover 32, 64 and 128", p->D);
-  if (p->G != 64 && p->G != 128 && !(p->G == 32 && p->D == 32 && full))
-    return set_error(INTFA_ERR_UNSUPPORTED, "G=%d unsupported: 64 or 128 (32 for full-int8 at head_dim 32)", p->G);
+  if (!head_dim_ok(p->D))
+    return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: 16, 32, 64, 128 or 256", p->D);
+  if (p->G != 64 && p->G != 128 && !(p->G == 32 && p->D <= 32 && full))
+    return set_error(INTFA_ERR_UNSUPPORTED, "G=%d unsupported: 64 or 128 (32 for full-int8 at head dims 16 and 32)", p->G);
+  if (p->D == 256 && p->G == 128 && !full)
+    return set_error(INTFA_ERR_UNSUPPORTED, "half-int8 at head_dim 256 runs with G=64 only");
   if (p->p_round != 0 && p->p_round != 1) return set_error(INTFA_ERR_INVALID_ARG, "p_round must be 0 or 1");
   if (p->H_kv < 0 || (p->H_kv > 0 && p->H % p->H_kv != 0))
     return set_error(INTFA_ERR_INVALID_ARG, "H=%d must be a multiple of H_kv=%d", p->H, p->H_kv);
   if (p->o_dtype != INTFA_OUT_FP16 && p->o_dtype != INTFA_OUT_BF16)
     return set_error(INTFA_ERR_INVALID_ARG, "o_dtype must be INTFA_OUT_FP16 or INTFA_OUT_BF16");
-  if ((long long)p->B * p->H * (((long long)p->Nq + 127) / 128) > 0x7fffffffLL) return set_error(INTFA_ERR_TOO_LARGE, "too many work items");
+  if ((long long)p->B * p->H * (((long long)p->Nq + 127) / 128) * (p->D == 256 ? 2 : 1) > 0x7fffffffLL) return set_error(INTFA_ERR_TOO_LARGE, "too many work items");
   int rc;
   if ((rc = check_tma_tensor("q", p->q, p->q_stride, 1))) return rc;
   if ((rc = check_tma_tensor("k", p->k, p->k_stride, 1))) return rc;
@@ -117,7 +122,7 @@ static int check_quant_args(const void* x, const int64_t* st, const void* x8, co
                             int D) {
   if (!x || !st || !x8 || !scale) return set_error(INTFA_ERR_INVALID_ARG, "NULL argument");
   if (B <= 0 || H <= 0 || N <= 0) return set_error(INTFA_ERR_INVALID_ARG, "B, H, N must be positive");
-  if (D != 32 && D != 64 && D != 128) return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: 32, 64 or 128", D);
+  if (!head_dim_ok(D)) return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: 16, 32, 64, 128 or 256", D);
   if (!aligned16(x) || st[0] % 8 || st[1] % 8 || st[2] % 8)
     return set_error(INTFA_ERR_INVALID_ARG, "input rows must be 16-byte aligned (pointer and strides multiples of 8 elements)");
   if (!aligned16(x8)) return set_error(INTFA_ERR_INVALID_ARG, "int8 output must be 16-byte aligned");
@@ -158,7 +163,7 @@ int intfa_quant_qkv(const void* q, const void* k, const void* v, const int64_t v
                     int32_t Nq, int32_t Nk, int32_t D, void* workspace, size_t workspace_bytes, void* stream) {
   if (!q || !k || !q8 || !k8 || !q_scale || !k_scale) return set_error(INTFA_ERR_INVALID_ARG, "NULL argument");
   if (B <= 0 || H <= 0 || H_kv <= 0 || Nq <= 0 || Nk <= 0) return set_error(INTFA_ERR_INVALID_ARG, "B, H, H_kv, Nq, Nk must be positive");
-  if (D != 32 && D != 64 && D != 128) return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: 32, 64 or 128", D);
+  if (!head_dim_ok(D)) return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: 16, 32, 64, 128 or 256", D);
   if (!aligned16(q) || !aligned16(k) || !aligned16(q8) || !aligned16(k8))
     return set_error(INTFA_ERR_INVALID_ARG, "q, k, q8, k8 must be 16-byte aligned (and contiguous)");
   if (v) {
@@ -179,7 +184,7 @@ int intfa_v_colmax(const void* v, const int64_t v_stride[3], void* colmax, int32
                    void* stream) {
   if (!v || !v_stride || !colmax) return set_error(INTFA_ERR_INVALID_ARG, "NULL argument");
   if (B <= 0 || H <= 0 || N <= 0) return set_error(INTFA_ERR_INVALID_ARG, "B, H, N must be positive");
-  if (D != 32 && D != 64 && D != 128) return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: 32, 64 or 128", D);
+  if (!head_dim_ok(D)) return set_error(INTFA_ERR_UNSUPPORTED, "head_dim %d unsupported: 16, 32, 64, 128 or 256", D);
   if (!aligned16(v) || v_stride[0] % 8 || v_stride[1] % 8 || v_stride[2] % 8)
     return set_error(INTFA_ERR_INVALID_ARG, "input rows must be 16-byte aligned (pointer and strides multiples of 8 elements)");
   if ((long long)B * H > 65535) return set_error(INTFA_ERR_TOO_LARGE, "B*H=%lld exceeds 65535", (long long)B * H);

@@ -6,7 +6,7 @@
 // reference's BLOCK_N, flash_atten_full_int8.py:30-70).
 //
 // One kernel family, intfa_fwd_pipe_kernel (intfa_fwd_pipe.cuh), serves full-int8 and half-int8 at head dims
-// 32, 64 and 128: one CTA of 512 threads per SM -- TMA producer, two MMA-issuing warps (S = Q K^T with tcgen05.mma
+// 16 to 256: one CTA of 512 threads per SM -- TMA producer, two MMA-issuing warps (S = Q K^T with tcgen05.mma
 // kind::i8 into int32 TMEM accumulators; O_j = P V with kind::i8, or kind::f16 for half-int8), two softmax groups
 // on alternate KV steps, accumulator warps.
 //
@@ -55,11 +55,17 @@ __device__ __forceinline__ uint32_t pack_out(float x, float y, int bf16) {
 
 struct TileInfo {
   int bh, b, h, hk, mb, work, nsteps;   // hk: the K/V head this query head reads (grouped-query attention)
+  int vh;                               // which D-wide slice of the V / output channels this pass covers (head dim 256: 0, 1)
 };
 
-template <bool RAGGED = false>
+template <bool RAGGED = false, int NVH = 1>
 __device__ __forceinline__ TileInfo decode_tile(const KParams& p, int tile, int G) {
   TileInfo t;
+  t.vh = 0;
+  if constexpr (NVH > 1) {
+    t.vh = tile % NVH;
+    tile /= NVH;
+  }
   t.bh = tile / p.MB;
   const int i = tile - t.bh * p.MB;
   t.mb = p.causal ? (p.MB - 1 - i) : i;       // causal: long rows first
@@ -160,24 +166,28 @@ static int make_tmap(CUtensorMap* tm, const void* base, int esize, const int64_t
 
 static inline int kv_heads(const IntfaFwdParams* a) { return a->H_kv > 0 ? a->H_kv : a->H; }
 
-// One CTA per SM.
-template <int D, int G, bool FULL, bool PRNE, bool RAGGED>
+static constexpr CUtensorMapSwizzle swizzle_of_row_bytes(int bytes) {
+  return bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+}
+
+// One CTA per SM.  The tensor maps describe the tensors with their own head dim (a->D); the boxes are as wide as the
+// kernel's tiles, so at head dim 16 the upper half of every 32-wide box lies outside the tensor and arrives as zeros.
+template <int D, int G, bool FULL, bool PRNE, bool RAGGED, int DQ = D>
 static int launch_pipe(const IntfaFwdParams* a, const KParams& kp, cudaStream_t stream) {
-  using C = PipeCfg<D, G, FULL>;
+  using C = PipeCfg<D, G, FULL, DQ>;
   static_assert(C::SMEM_BYTES <= 227 * 1024, "shared memory");
   CUtensorMap tmQ, tmK, tmV;
-  const CUtensorMapSwizzle swzD = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B
-                                  : (D == 64) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+  const CUtensorMapSwizzle swzQK = swizzle_of_row_bytes(C::QK_ROWB), swzV = swizzle_of_row_bytes(C::V_ROWB);
+  const int hd = a->D;
   int rc;
-  if ((rc = make_tmap(&tmQ, a->q, 1, a->q_stride, a->B, a->H, a->Nq, D, D, kBM, swzD))) return rc;
-  if ((rc = make_tmap(&tmK, a->k, 1, a->k_stride, a->B, kv_heads(a), a->Nk, D, D, G, swzD))) return rc;
+  if ((rc = make_tmap(&tmQ, a->q, 1, a->q_stride, a->B, a->H, a->Nq, hd, C::QK_ROWB, kBM, swzQK))) return rc;
+  if ((rc = make_tmap(&tmK, a->k, 1, a->k_stride, a->B, kv_heads(a), a->Nk, hd, C::QK_ROWB, G, swzQK))) return rc;
   if constexpr (FULL) {
-    if ((rc = make_tmap(&tmV, a->v, 1, a->v_stride, a->B, kv_heads(a), a->Nk, D, D, G, swzD))) return rc;
+    if ((rc = make_tmap(&tmV, a->v, 1, a->v_stride, a->B, kv_heads(a), a->Nk, hd, D, G, swzV))) return rc;
   } else {
-    if ((rc = make_tmap(&tmV, a->v, 2, a->v_stride, a->B, kv_heads(a), a->Nk, D, D >= 64 ? 64 : D, G,
-                        D >= 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
+    if ((rc = make_tmap(&tmV, a->v, 2, a->v_stride, a->B, kv_heads(a), a->Nk, hd, D >= 64 ? 64 : D, G, swzV))) return rc;
   }
-  auto kern = intfa_fwd_pipe_kernel<D, G, FULL, PRNE, RAGGED>;
+  auto kern = intfa_fwd_pipe_kernel<D, G, FULL, PRNE, RAGGED, DQ>;
   static std::atomic<bool> attr_done[64];     // per instantiation and device (the attribute is per device)
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return set_error(INTFA_ERR_CUDA, "cannot query the current device");
@@ -207,6 +217,7 @@ int fwd_dispatch(const IntfaFwdParams* a, cudaStream_t stream) {
   kp.ks_sb = a->ks_stride[0]; kp.ks_sh = a->ks_stride[1];
   kp.vs_sb = a->vs_stride[0]; kp.vs_sh = a->vs_stride[1]; kp.vs_sd = a->vs_stride[2];
   kp.B = a->B; kp.H = a->H; kp.Nq = a->Nq; kp.Nk = a->Nk;
+  kp.dh = a->D;
   kp.hk_ratio = a->H / kv_heads(a);
   kp.o_bf16 = a->o_dtype == INTFA_OUT_BF16 ? 1 : 0;
   kp.causal = a->causal ? 1 : 0;
@@ -228,26 +239,32 @@ int fwd_dispatch(const IntfaFwdParams* a, cudaStream_t stream) {
   // Sequence lengths that are not multiples of the tile sizes run the instantiation that masks the last tiles
   // (so do calls with one v_scale row per KV tile: the code for them is compiled into that instantiation only)
   const bool ragged = (a->Nq % kBM) != 0 || (a->Nk % a->G) != 0 || a->vs_stride_blk != 0;
-#define INTFA_CASE(DD, GG)                                                                               \
-  if (D == DD && G == GG) {                                                                              \
-    if (full && ragged) return rne ? launch_pipe<DD, GG, true, true, true>(a, kp, stream)                \
-                                   : launch_pipe<DD, GG, true, false, true>(a, kp, stream);              \
-    if (full) return rne ? launch_pipe<DD, GG, true, true, false>(a, kp, stream)                         \
-                         : launch_pipe<DD, GG, true, false, false>(a, kp, stream);                       \
-    if constexpr (GG >= 64) {                                                                            \
-      return ragged ? launch_pipe<DD, GG, false, false, true>(a, kp, stream)                             \
-                    : launch_pipe<DD, GG, false, false, false>(a, kp, stream);                           \
+  // HD: head dim of the call; DD, DQ: the kernel's tile width and Q/K width for it; HALF: half-int8 built for this G
+#define INTFA_CASE(HD, DD, GG, DQ, HALF)                                                                 \
+  if (D == HD && G == GG) {                                                                              \
+    if (full && ragged) return rne ? launch_pipe<DD, GG, true, true, true, DQ>(a, kp, stream)            \
+                                   : launch_pipe<DD, GG, true, false, true, DQ>(a, kp, stream);          \
+    if (full) return rne ? launch_pipe<DD, GG, true, true, false, DQ>(a, kp, stream)                     \
+                         : launch_pipe<DD, GG, true, false, false, DQ>(a, kp, stream);                   \
+    if constexpr (HALF) {                                                                                \
+      return ragged ? launch_pipe<DD, GG, false, false, true, DQ>(a, kp, stream)                         \
+                    : launch_pipe<DD, GG, false, false, false, DQ>(a, kp, stream);                       \
     }                                                                                                    \
   }
-  INTFA_CASE(128, 128)
-  INTFA_CASE(128, 64)
-  INTFA_CASE(64, 64)
-  INTFA_CASE(64, 128)
-  INTFA_CASE(32, 32)      // G = 32: full-int8 only (fp16 P tiles need 64 columns)
-  INTFA_CASE(32, 64)
-  INTFA_CASE(32, 128)
+  INTFA_CASE(128, 128, 128, 128, true)
+  INTFA_CASE(128, 128, 64, 128, true)
+  INTFA_CASE(64, 64, 64, 64, true)
+  INTFA_CASE(64, 64, 128, 64, true)
+  INTFA_CASE(32, 32, 32, 32, false)      // G = 32: full-int8 only (fp16 P tiles need 64 columns)
+  INTFA_CASE(32, 32, 64, 32, true)
+  INTFA_CASE(32, 32, 128, 32, true)
+  INTFA_CASE(16, 32, 32, 32, false)      // head dim 16: the 32-wide kernel on zero-filled tiles
+  INTFA_CASE(16, 32, 64, 32, true)
+  INTFA_CASE(16, 32, 128, 32, true)
+  INTFA_CASE(256, 128, 128, 256, false)  // head dim 256: two passes of 128 V channels; fp16 V tiles at G = 128 do not fit
+  INTFA_CASE(256, 128, 64, 256, true)
 #undef INTFA_CASE
-  return set_error(INTFA_ERR_UNSUPPORTED, "unsupported (D=%d, G=%d, %s): supported are D in {64,128} with G in {64,128}, and D=32 with G in {32,64,128} (G=32: full-int8 only)", D, G, full ? "full-int8" : "half-int8");
+  return set_error(INTFA_ERR_UNSUPPORTED, "unsupported (D=%d, G=%d, %s): G is 64 or 128 (32 too for full-int8 at head dims 16 and 32; half-int8 at head dim 256: 64 only)", D, G, full ? "full-int8" : "half-int8");
 }
 
 }  // namespace intfa

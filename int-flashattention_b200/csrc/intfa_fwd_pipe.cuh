@@ -1,24 +1,27 @@
-// INT8 attention forward, pipelined kernel (full-int8 and half-int8): ONE CTA per SM, one 128-row query tile at a time.
+// INT8 attention forward (full-int8 and half-int8): ONE CTA per SM, one 128-row query tile at a time.
 // (Included by intfa_fwd.cu inside namespace intfa, after the shared helpers.)
 //
-// 640 threads:
-//   warp 0        TMA producer (Q once per work item; K, V and the K-scale slice through an NS-stage ring)
-//   warp 1        MMA issuer (whole warp runs the loop, one elected lane issues)
-//   warp 2        TMEM allocator; warp 3 idle
+// 512 threads:
+//   warp 0        TMA producer (Q once per work item; K and V through rings of shared-memory stages, the K-scale
+//                 slices through a ring of their own); it also draws the work items from the global counter
+//   warp 1        MMA issuer for S = Q K^T (whole warp runs the loop, one elected lane issues): up to three KV steps
+//                 ahead of the softmax groups, into S buffer (step mod 3)
+//   warp 2        TMEM allocator
+//   warp 3        MMA issuer for O_j = P V
 //   warps 4-7     softmax group 0, warps 8-11 softmax group 1: one thread per query row.  The groups take
 //                 ALTERNATE KV steps (group g owns the steps whose running index is g mod 2), each with its own
-//                 S buffer in TMEM and its own P buffer in shared memory, so that on every scheduler one
-//                 warp is in pass A (dequantise, row max: FMA pipe) while the other is in pass B (exp2, P:
-//                 MUFU).  The running max m and row sum l of a row travel between the two threads that own
-//                 it through shared memory, once per step each.
-//   warps 12-19   accumulator update and epilogue, two threads per query row (half the channels each):
-//                 full-int8: acc = acc*alpha + fp32(O_j)*s_v/127 with acc (fp32) and O_j (int32) both in TMEM;
-//                 half-int8: P V (fp16 MMA) accumulates straight into acc, these warps multiply the row by
-//                 alpha beforehand when some alpha of the warp's 32 rows is not 1.
-// TMEM columns: S0 [0,G) | S1 [G,2G) | O_j [2G, 2G+D) | acc [2G+D, 2G+2D)  (<= 512); half-int8: no O_j, acc at 2G.
+//                 P buffer in shared memory, so that on every scheduler one warp is in pass A (dequantise, row
+//                 max: FMA pipe) while the other is in pass B (exp2, P: exp2 unit).  The running max m of a row
+//                 travels between the two threads that own it through shared memory, once per step.
+//   warps 12-15   accumulator update and epilogue, one thread per query row:
+//                 full-int8: A = A*alpha + fp32(O_j) with the fp32 row A in REGISTERS and O_j (int32) in TMEM;
+//                 half-int8: P V (fp16 MMA) accumulates straight into an fp32 accumulator in TMEM, these warps
+//                 multiply the row by alpha beforehand when some alpha of the warp's 32 rows is not 1.
+//                 They also carry the row sum l = l*alpha + rowsum(P) (see PipeCfg::L_IN_ACC).
+// TMEM columns: S0 [0,G) | S1 [G,2G) | S2 [2G,3G) | O_j, or the half-int8 accumulator [3G, 3G+D)  (<= 512).
 // S and O_j are int32 accumulators that start each KV step from the bit pattern of 1.5*2^23, written by a
 // small fp16 MMA ahead of the int8 MMAs, so that the threads read fp32(S32) + 1.5*2^23 without a conversion.
-// Arithmetic is the same as in intfa_fwd_kernel (see the contract at the top of intfa_fwd.cu).
+// The arithmetic contract is at the top of intfa_fwd.cu.
 #pragma once
 
 constexpr int kPipeThreads = 512;
@@ -31,15 +34,24 @@ constexpr int kPipeServiceRegs = 40, kPipeSoftmaxRegs = 136, kPipeCorrRegs = 184
 static_assert(128 * kPipeServiceRegs + kPipeSoftmaxThreads * kPipeSoftmaxRegs + kPipeCorrThreads * kPipeCorrRegs <=
                   kPipeThreads * kPipeLaunchRegs, "setmaxnreg budget exceeds the registers the CTA is launched with");
 
-template <int D, int G, bool FULL>
+// D: channels of V and of the accumulator that one pass covers (and the width the tensor-core tiles are built for);
+// DQ: head dim of Q and K.  DQ == D except at head dim 256, which runs as DQ = 256, D = 128: every query tile is
+// taken twice in a row by the same CTA, once per half of the V channels (the accumulator row of one thread and the
+// TMEM columns hold 128 channels); S, the running max and P are the same in both passes.
+template <int D, int G, bool FULL, int DQ = D>
 struct PipeCfg {
-  static constexpr int Q_BYTES = kBM * D;
-  static constexpr int K_BYTES = G * D;
+  static_assert(DQ == D || (DQ == 256 && D == 128), "head dims");
+  static constexpr int NVH = DQ / D;                               // passes per query tile
+  static constexpr int QK_ROWB = DQ < 128 ? DQ : 128;              // Q and K sit in shared memory as panels of [rows][QK_ROWB bytes]
+  static constexpr int QK_PANELS = DQ / QK_ROWB;
+  static constexpr int Q_BYTES = kBM * DQ;
+  static constexpr int K_BYTES = G * DQ;
   static constexpr int V_BYTES = FULL ? G * D : G * D * 2;         // int8, or fp16 as D/64 boxes of [G keys][64 channels]
   static constexpr int P_BYTES = FULL ? kBM * G : kBM * G * 2;     // int8, or fp16 as G/64 blocks of [128 rows][64 columns]
   static constexpr int KS_BYTES = G * 4;
-  static constexpr int NSK = 4;                                    // K stages
-  static constexpr int NSV = (FULL || G == 64) ? 4 : 2;            // V stages (fp16 V tiles are twice the size)
+  static constexpr bool BIG = DQ > 128 && G == 128;                // 32 KB K tiles: three stages are what fits
+  static constexpr int NSK = BIG ? 3 : 4;                          // K stages
+  static constexpr int NSV = BIG ? 3 : (FULL || G == 64) ? 4 : 2;  // V stages (fp16 V tiles are twice the size)
   static constexpr int NKS = 8;                                    // K-scale slots: a slot is rewritten 8 steps later, when
                                                                    // the three S buffers have long forced its step out
   static constexpr int NSB = 3;                                    // S buffers in TMEM
@@ -71,8 +83,10 @@ struct PipeCfg {
   static_assert(NSB * G + D <= 512, "TMEM columns");
   static constexpr int TMEM_COLS = 512;
   static_assert(FULL || G >= 64, "half-int8: fp16 P tiles are built from 64-column blocks");
-  static constexpr uint64_t SWZ_QK = (D == 128) ? kSwz128 : (D == 64) ? kSwz64 : kSwz32;       // Q, K rows are D bytes
-  static constexpr uint32_t SBO_QK = 8 * D;
+  static constexpr uint64_t SWZ_QK = (QK_ROWB == 128) ? kSwz128 : (QK_ROWB == 64) ? kSwz64 : kSwz32;
+  static constexpr uint32_t SBO_QK = 8 * QK_ROWB;
+  // start-address offset (16-byte units) of the kk-th 32-byte K slice of a [ROWS][DQ] operand
+  __host__ __device__ static constexpr uint32_t qk_slice(int kk, int rows) { return (uint32_t)((kk / 4) * ((rows * QK_ROWB) >> 4) + 2 * (kk % 4)); }
   static constexpr uint64_t SWZ_P = FULL ? ((G == 128) ? kSwz128 : (G == 64) ? kSwz64 : kSwz32) : kSwz128;
   static constexpr uint32_t SBO_P = FULL ? 8 * G : 1024;
   // V rows: D bytes (int8), or boxes of min(D, 64) fp16 channels = 128 / 64 bytes
@@ -92,12 +106,12 @@ enum PipeWait { PW_TILE = 32, PW_QE, PW_KE, PW_VE, PW_QF, PW_KF, PW_VF, PW_SFREE
 
 // RAGGED: Nq / Nk are not multiples of 128 / G -- the last query tile and the last KV step are partial.  A separate
 // instantiation, so that the code of the common case stays as small as it was (instruction cache).
-template <int D, int G, bool FULL, bool PRNE, bool RAGGED>
+template <int D, int G, bool FULL, bool PRNE, bool RAGGED, int DQ = D>
 __global__ void __launch_bounds__(kPipeThreads, 1)
 intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const KParams p) {
-  using C = PipeCfg<D, G, FULL>;
-  constexpr int NSK = C::NSK, NSV = C::NSV, NSB = C::NSB;
+  using C = PipeCfg<D, G, FULL, DQ>;
+  constexpr int NSK = C::NSK, NSV = C::NSV, NSB = C::NSB, NVH = C::NVH;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5;
@@ -111,12 +125,12 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   constexpr int B_PFULL = 4;      // [2] softmax group b (4 warps): P in shared-memory buffer b, and S buffer b read out
   constexpr int B_PFREE = 6;      // [2] commit: the P V that read P buffer b is done
   constexpr int B_OFULL = 8;      // commit: O_j = P V in TMEM
-  constexpr int B_OFREE = 9;      // updater (8 warps): O_j read out
+  constexpr int B_OFREE = 9;      // accumulator warps (4): O_j read out
   constexpr int B_HL = 16;        // [2] !L_IN_ACC: softmax group g (4 warps): row sum after its step published
   constexpr int B_FIN = 10;       // [2] softmax (4 warps of one group): final (m, l) of the work item published; one
                                   //     barrier per slot, so that a short next work item cannot complete it twice
                                   //     before a slow accumulator warp has waited for the first completion
-  constexpr int B_FINFREE = 12;   // [2] updater (8 warps): it has read them
+  constexpr int B_FINFREE = 12;   // [2] accumulator warps (4): they have read them
   constexpr int B_HM = 14;        // [2] softmax group g (4 warps): running max after its step published
   constexpr int B_KFULL = 18, B_KEMPTY = 18 + NSK, B_VFULL = 18 + 2 * NSK, B_VEMPTY = 18 + 2 * NSK + NSV;
   constexpr int B_TILE = 18 + 2 * NSK + 2 * NSV, B_TDONE = B_TILE + 4;
@@ -192,7 +206,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   __syncthreads();
   const uint64_t descArm = make_smem_desc(smem_u32(smem + C::OFF_MAGIC), 128, 256, 0);
 
-  // work items: drawn from a global counter by the producer, published in a 4-slot ring (as in intfa_fwd_kernel)
+  // work items: drawn from a global counter by the producer, published in a 4-slot ring
   auto next_tile = [&](uint32_t& seq, bool ack, bool whole_warp) -> int {
     const uint32_t slot = seq & 3u, par = (seq >> 2) & 1u;
     ++seq;
@@ -215,24 +229,39 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       prefetch_tmap(&tmK);
       prefetch_tmap(&tmV);
       uint32_t kv_it = 0, tile_it = 0, tseq = 0;
+      int drawn = 0, passes_left = 0;      // NVH > 1: the query tile in hand and how many of its passes are still to publish
       bool ok = true;
       while (ok) {
         if (tseq >= 4u) {
           ok = mbar_wait(BAR(B_TDONE + (tseq & 3u)), ((tseq >> 2) - 1u) & 1u, abort_flag, p.status, code_hi | PW_TILE);
           if (!ok) break;
         }
-        int tile = (int)atomicAdd(p.tile_counter, 1u);
-        if (tile >= p.num_tiles) tile = -1;
+        int tile;
+        if (NVH > 1 && passes_left > 0) {
+          tile = drawn * NVH + (NVH - passes_left);      // the next pass over the same query tile, on this CTA
+          --passes_left;
+        } else {
+          tile = (int)atomicAdd(p.tile_counter, 1u);
+          if (tile >= p.num_tiles) {
+            tile = -1;
+          } else if (NVH > 1) {
+            drawn = tile;
+            tile *= NVH;
+            passes_left = NVH - 1;
+          }
+        }
         tile_slot[tseq & 3u] = tile;
         mbar_arrive(BAR(B_TILE + (tseq & 3u)));
         ++tseq;
         if (tile < 0) break;
-        const TileInfo t = decode_tile<RAGGED>(p, tile, G);
+        const TileInfo t = decode_tile<RAGGED, NVH>(p, tile, G);
         if (t.nsteps == 0) continue;
         ok = mbar_wait(BAR(B_QEMPTY), (tile_it & 1) ^ 1, abort_flag, p.status, code_hi | PW_QE);
         if (!ok) break;
         mbar_expect_tx(BAR(B_QFULL), C::Q_BYTES);
-        tma_load_4d(sQ, &tmQ, BAR(B_QFULL), 0, t.mb * kBM, t.h, t.b);
+#pragma unroll
+        for (int pn = 0; pn < C::QK_PANELS; ++pn)
+          tma_load_4d(sQ + pn * (kBM * C::QK_ROWB), &tmQ, BAR(B_QFULL), pn * C::QK_ROWB, t.mb * kBM, t.h, t.b);
         const float* ks_row = p.ks + (long long)t.b * p.ks_sb + (long long)t.hk * p.ks_sh;
         for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
           const uint32_t s = kv_it % NSK, ph = (kv_it / NSK) & 1;
@@ -241,7 +270,9 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           const int jb = kv_tile_of_step(p, j, t.nsteps);
           if (p.skip_k_load == 0 || kv_it + 1 != (uint32_t)p.skip_k_load) {      // (test hook: a K tile that never arrives)
             mbar_expect_tx(BAR(B_KFULL + s), C::K_BYTES + C::KS_BYTES);
-            tma_load_4d(sK + s * C::K_BYTES, &tmK, BAR(B_KFULL + s), 0, jb * G, t.hk, t.b);
+#pragma unroll
+            for (int pn = 0; pn < C::QK_PANELS; ++pn)
+              tma_load_4d(sK + s * C::K_BYTES + pn * (G * C::QK_ROWB), &tmK, BAR(B_KFULL + s), pn * C::QK_ROWB, jb * G, t.hk, t.b);
             bulk_load_1d(sKS + (kv_it % C::NKS) * C::KS_BYTES, ks_row + jb * G, C::KS_BYTES, BAR(B_KFULL + s));
           }
           const uint32_t sv = kv_it % NSV, phv = (kv_it / NSV) & 1;
@@ -249,11 +280,11 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           if (!ok) break;
           mbar_expect_tx(BAR(B_VFULL + sv), C::V_BYTES);
           if constexpr (FULL) {
-            tma_load_4d(sV + sv * C::V_BYTES, &tmV, BAR(B_VFULL + sv), 0, jb * G, t.hk, t.b);
+            tma_load_4d(sV + sv * C::V_BYTES, &tmV, BAR(B_VFULL + sv), t.vh * D, jb * G, t.hk, t.b);
           } else {
 #pragma unroll
             for (int c = 0; c < C::V_BOXES; ++c)
-              tma_load_4d(sV + sv * C::V_BYTES + c * (G * 128), &tmV, BAR(B_VFULL + sv), c * 64, jb * G, t.hk, t.b);
+              tma_load_4d(sV + sv * C::V_BYTES + c * (G * 128), &tmV, BAR(B_VFULL + sv), t.vh * D + c * 64, jb * G, t.hk, t.b);
           }
         }
         ++tile_it;
@@ -276,7 +307,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       while (ok) {
         const int tile = next_tile(tseq, lane == 0, true);
         if (tile < 0) break;
-        const TileInfo t = decode_tile<RAGGED>(p, tile, G);
+        const TileInfo t = decode_tile<RAGGED, NVH>(p, tile, G);
         if (t.nsteps == 0) continue;
         ok = mbar_wait_warp(BAR(B_QFULL), tile_it & 1, abort_flag, p.status, code_hi | PW_QF);
         if (!ok) break;
@@ -297,7 +328,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           if (elect_one()) {
             umma_f16(tSb, descArm, descArm, C::IDESC_ARM_S, 0);
 #pragma unroll
-            for (int kk = 0; kk < D / 32; ++kk) umma_i8(tSb, descQ0 + 2 * kk, bd0 + 2 * kk, C::IDESC_QK, 1);
+            for (int kk = 0; kk < DQ / 32; ++kk) umma_i8(tSb, descQ0 + C::qk_slice(kk, kBM), bd0 + C::qk_slice(kk, G), C::IDESC_QK, 1);
             umma_commit(BAR(B_SFULL + sb));
             umma_commit(BAR(B_KEMPTY + s));
             if (j + 1 == t.nsteps) umma_commit(BAR(B_QEMPTY));
@@ -320,7 +351,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       while (ok) {
         const int tile = next_tile(tseq, lane == 0, true);
         if (tile < 0) break;
-        const TileInfo t = decode_tile<RAGGED>(p, tile, G);
+        const TileInfo t = decode_tile<RAGGED, NVH>(p, tile, G);
         for (int j = 0; j < t.nsteps; ++j, ++kv_it) {
           const uint32_t s = kv_it % NSV, ph = (kv_it / NSV) & 1;
           const uint32_t b = kv_it & 1;

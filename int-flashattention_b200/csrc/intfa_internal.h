@@ -15,6 +15,8 @@ struct KParams {
   long long o_sb, o_sh, o_sn;
   long long qs_sb, qs_sh, ks_sb, ks_sh, vs_sb, vs_sh, vs_sd;
   int B, H, Nq, Nk;
+  int dh;                        // head dim of the tensors in memory (16 runs the 32-wide kernel on zero-filled tiles,
+                                 // 256 the 128-wide one twice per query tile, once per half of the V channels)
   int hk_ratio;                  // query heads per K/V head (1 unless grouped-query attention)
   int o_bf16;                    // output element type: 0 fp16, 1 bf16
   int causal;

@@ -6,7 +6,7 @@
 //   scale = fp16( fp32(amax) / 127 )      (IEEE fp32 division, then round-to-nearest fp16)
 //   q     = int8( rint( fp16( fp32(x) / fp32(scale) ) ) )   (rint = half-to-even, as torch.round)
 // The per-element division is evaluated as a correctly rounded quotient from one reciprocal per
-// row/channel and two fmas (see quant_byte), so it costs no division instruction per element.
+// row/channel and two fmas (see quant_pair), so it costs no division instruction per element.
 // Scales are written as fp32 holding the fp16-representable value.  amax == 0 gives
 // scale 0 and q 0 (the reference computes 0/0 there).
 //
@@ -22,6 +22,7 @@
 #include <atomic>
 
 #include "intfa_internal.h"
+#include "intfa_ptx.cuh"
 
 namespace intfa {
 
@@ -31,32 +32,43 @@ __device__ __forceinline__ float scale_from_amax(float amax) {
 // Correctly rounded x / s without a division per element (Markstein): with r = RN(1/s),
 // q0 = RN(x*r), e = x - q0*s (exact in one fma), q = RN(q0 + e*r) equals RN(x/s) unless the
 // significand of s is all ones -- impossible here because s is an fp16 value held in fp32.
-// Then the reference's rounding chain: fp16(q), and rint() done by adding 1.5*2^23, which also
-// leaves the two's-complement integer in the low byte of the sum.
-__device__ __forceinline__ uint32_t quant_byte(float x, float s, float r) {
-  const float q0 = x * r;
-  const float e = fmaf(-q0, s, x);
-  const float q = fmaf(e, r, q0);
-  const float t = __half2float(__float2half_rn(q));
-  const uint32_t u = __float_as_uint(t + 12582912.0f);
-  return s == 0.f ? 0u : (u & 0xffu);
+// Then the reference's rounding chain: fp16(q), and rint() done IN fp16 by adding 1536 = 1.5*2^10 (the sum has
+// an ulp of 1, so its round-to-nearest-even is rint, and its bit pattern is 0x6600 + n: the two's-complement
+// integer is the low byte).  Everything runs two elements per instruction (packed fp32, fp16x2): these kernels
+// are as much bound by instruction issue as by HBM.
+// A zero scale (an all-zero row or channel; the reference computes 0/0 there) is given the reciprocal 0, which makes
+// every quotient 0.
+struct Scale2 { uint64_t neg_s, r; };      // (-s, -s') and (1/s, 1/s') of two neighbouring elements
+__device__ __forceinline__ float safe_rcp(float s) { return s == 0.f ? 0.f : __frcp_rn(s); }
+__device__ __forceinline__ Scale2 make_scale2(float s0, float s1) {
+  Scale2 k;
+  k.neg_s = f2_pack(-s0, -s1);
+  k.r = f2_pack(safe_rcp(s0), safe_rcp(s1));
+  return k;
+}
+// two fp16 inputs -> two int8 in bytes 0 and 2 of the result
+__device__ __forceinline__ uint32_t quant_pair(__half2 x, const Scale2& k) {
+  const float2 f = __half22float2(x);
+  const uint64_t X = f2_pack(f.x, f.y);
+  const uint64_t q0 = f2_mul(X, k.r);
+  const uint64_t e = f2_fma(q0, k.neg_s, X);
+  float qa, qb;
+  f2_unpack(f2_fma(e, k.r, q0), qa, qb);
+  const __half2 t = __floats2half2_rn(qa, qb);
+  const __half2 u = __hadd2(t, __half2(__ushort_as_half(0x6600), __ushort_as_half(0x6600)));
+  return *reinterpret_cast<const uint32_t*>(&u);
 }
 __device__ __forceinline__ float amax8(const uint4& v) {
   const __half2* h = reinterpret_cast<const __half2*>(&v);
   __half2 m = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
   return fmaxf(__low2float(m), __high2float(m));
 }
-// s[i], r[i] = scale and its correctly rounded reciprocal for element i of the 8
-__device__ __forceinline__ uint2 quant8(const uint4& v, const float* s, const float* r) {
+// k[i]: the scales of elements 2i, 2i+1 of the 8
+__device__ __forceinline__ uint2 quant8(const uint4& v, const Scale2 (&k)[4]) {
   const __half2* h2 = reinterpret_cast<const __half2*>(&v);
-  uint32_t w[2] = {0u, 0u};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 f = __half22float2(h2[i]);
-    w[i >> 1] |= quant_byte(f.x, s[2 * i], r[2 * i]) << (16 * (i & 1));
-    w[i >> 1] |= quant_byte(f.y, s[2 * i + 1], r[2 * i + 1]) << (16 * (i & 1) + 8);
-  }
-  return make_uint2(w[0], w[1]);
+  const uint32_t u0 = quant_pair(h2[0], k[0]), u1 = quant_pair(h2[1], k[1]);
+  const uint32_t u2 = quant_pair(h2[2], k[2]), u3 = quant_pair(h2[3], k[3]);
+  return make_uint2(__byte_perm(u0, u1, 0x6420), __byte_perm(u2, u3, 0x6420));
 }
 
 // L2 residency hints.  The first launch of the fused prologue reads V for its column maxima and the second reads it
@@ -126,10 +138,9 @@ __device__ __forceinline__ void pertoken_rows(const __half* __restrict__ x, long
       for (int o = LPR / 2; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
       const float s = scale_from_amax(a);
       if (rows[u] < total_rows) {
-        const float rcp = __frcp_rn(s);
-        const float sv[8] = {s, s, s, s, s, s, s, s};
-        const float rv[8] = {rcp, rcp, rcp, rcp, rcp, rcp, rcp, rcp};
-        st_hint(x8 + rows[u] * D + sub * 8, quant8(v[u], sv, rv), once);
+        const Scale2 k1 = make_scale2(s, s);
+        const Scale2 k[4] = {k1, k1, k1, k1};
+        st_hint(x8 + rows[u] * D + sub * 8, quant8(v[u], k), once);
         if (sub == 0) scale[rows[u]] = s;
       }
     }
@@ -243,18 +254,21 @@ __global__ void __launch_bounds__(256) v_quant_kernel(const __half* __restrict__
   const uint64_t once = l2_policy_evict_first();
   if (threadIdx.x < 32) {
     // every channel's absmax; for the per-(batch,head) mode reduce them to one
-    float a[D / 32];
+    constexpr int CPL = (D + 31) / 32;     // channels per lane
+    float a[CPL];
     float all = 0.f;
 #pragma unroll
-    for (int i = 0; i < D / 32; ++i) {
+    for (int i = 0; i < CPL; ++i) {
       a[i] = 0.f;      // colmax is [nparts][B*H][D]: one row, or the partial maxima of the fused first launch
-      for (int c = 0; c < nparts; ++c) a[i] = fmaxf(a[i], __uint_as_float(colmax[((long long)c * gridDim.y + bh) * D + lane + 32 * i]));
+      if (lane + 32 * i < D)
+        for (int c = 0; c < nparts; ++c) a[i] = fmaxf(a[i], __uint_as_float(colmax[((long long)c * gridDim.y + bh) * D + lane + 32 * i]));
       all = fmaxf(all, a[i]);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) all = fmaxf(all, __shfl_xor_sync(0xffffffffu, all, o));
 #pragma unroll
-    for (int i = 0; i < D / 32; ++i) s_scale[lane + 32 * i] = scale_from_amax(per_channel ? a[i] : all);
+    for (int i = 0; i < CPL; ++i)
+      if (lane + 32 * i < D) s_scale[lane + 32 * i] = scale_from_amax(per_channel ? a[i] : all);
   }
   __syncthreads();
   if (blockIdx.x == 0) {
@@ -264,12 +278,9 @@ __global__ void __launch_bounds__(256) v_quant_kernel(const __half* __restrict__
       scale[bh] = s_scale[0];
     }
   }
-  float sv[8], rv[8];
+  Scale2 k[4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    sv[i] = s_scale[sub * 8 + i];
-    rv[i] = __frcp_rn(sv[i]);
-  }
+  for (int i = 0; i < 4; ++i) k[i] = make_scale2(s_scale[sub * 8 + 2 * i], s_scale[sub * 8 + 2 * i + 1]);
   const __half* base = x + b * sB + h * sH + sub * 8;
   int8_t* obase = x8 + (long long)bh * N * D + sub * 8;
   const int r_begin = blockIdx.x * rows_per_cta;
@@ -284,7 +295,7 @@ __global__ void __launch_bounds__(256) v_quant_kernel(const __half* __restrict__
 #pragma unroll
     for (int u = 0; u < kQuantUnroll; ++u) {
       const int r = r0 + u * nw * RPW;
-      if (r < r_end) st_hint(obase + (long long)r * D, quant8(v[u], sv, rv), once);
+      if (r < r_end) st_hint(obase + (long long)r * D, quant8(v[u], k), once);
     }
   }
 }
@@ -293,6 +304,16 @@ __global__ void scales_f16_to_f32_kernel(const __half* __restrict__ src, float* 
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     dst[i] = __half2float(src[i]);
 }
+
+// head dims of the reference's ops (flash_atten_full_int8.py:193): one instantiation each
+#define INTFA_D_SWITCH(D, CALL)                 \
+  switch (D) {                                  \
+    case 16: { constexpr int DD = 16; CALL; } break;   \
+    case 32: { constexpr int DD = 32; CALL; } break;   \
+    case 64: { constexpr int DD = 64; CALL; } break;   \
+    case 128: { constexpr int DD = 128; CALL; } break; \
+    default: { constexpr int DD = 256; CALL; } break;  \
+  }
 
 static int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
@@ -310,15 +331,9 @@ int quant_pertoken(const void* x, const int64_t* st, void* x8, float* scale, int
   const int grid = (int)(want < (long long)sms * 8 ? (want < 1 ? 1 : want) : (long long)sms * 8);
   if (rows >= (1LL << 31)) return set_error(INTFA_ERR_TOO_LARGE, "quant_pertoken: B*H*N must be below 2^31");
   const bool contig = st[2] == D && st[1] == (int64_t)N * D && st[0] == (int64_t)H * N * D;
-#define INTFA_QPT(DD, CC) \
+#define INTFA_QPT(CC) \
   quant_pertoken_kernel<DD, CC><<<grid, 256, 0, stream>>>((const __half*)x, st[0], st[1], st[2], (int8_t*)x8, scale, H, N, rows)
-  if (D == 128) {
-    if (contig) INTFA_QPT(128, true); else INTFA_QPT(128, false);
-  } else if (D == 64) {
-    if (contig) INTFA_QPT(64, true); else INTFA_QPT(64, false);
-  } else {
-    if (contig) INTFA_QPT(32, true); else INTFA_QPT(32, false);
-  }
+  INTFA_D_SWITCH(D, if (contig) INTFA_QPT(true); else INTFA_QPT(false))
 #undef INTFA_QPT
   return check_launch("quant_pertoken");
 }
@@ -338,12 +353,7 @@ int v_colmax(const void* v, const int64_t* st, void* colmax, int B, int H, int N
   if (sms <= 0) return set_error(INTFA_ERR_CUDA, "cannot query SM count");
   int rows_per_cta;
   dim3 grid(v_grid(B * H, N, sms, &rows_per_cta), B * H);
-  if (D == 128)
-    v_colmax_kernel<128><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (unsigned int*)colmax, H, N, rows_per_cta);
-  else if (D == 64)
-    v_colmax_kernel<64><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (unsigned int*)colmax, H, N, rows_per_cta);
-  else
-    v_colmax_kernel<32><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (unsigned int*)colmax, H, N, rows_per_cta);
+  INTFA_D_SWITCH(D, (v_colmax_kernel<DD><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (unsigned int*)colmax, H, N, rows_per_cta)))
   return check_launch("v_colmax");
 }
 
@@ -354,12 +364,7 @@ static int v_quant_launch(const void* v, const int64_t* st, const void* colmax, 
   int rows_per_cta;
   dim3 grid(v_grid(B * H, N, sms, &rows_per_cta), B * H);
   const int pc = mode == INTFA_VSCALE_PER_CHANNEL;
-  if (D == 128)
-    v_quant_kernel<128><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (const unsigned int*)colmax, (int8_t*)v8, scale, pc, H, N, rows_per_cta, nparts);
-  else if (D == 64)
-    v_quant_kernel<64><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (const unsigned int*)colmax, (int8_t*)v8, scale, pc, H, N, rows_per_cta, nparts);
-  else
-    v_quant_kernel<32><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (const unsigned int*)colmax, (int8_t*)v8, scale, pc, H, N, rows_per_cta, nparts);
+  INTFA_D_SWITCH(D, (v_quant_kernel<DD><<<grid, 256, 0, stream>>>((const __half*)v, st[0], st[1], st[2], (const unsigned int*)colmax, (int8_t*)v8, scale, pc, H, N, rows_per_cta, nparts)))
   return check_launch("v_quant");
 }
 
@@ -404,9 +409,7 @@ int quant_qkv(const void* q, const void* k, const void* v, const int64_t* v_st, 
     gv = j.chunks * B * Hkv;
   }
   const int grid = j.gq + j.gk + gv;
-  if (D == 128) quant_qkv_kernel<128><<<grid, 256, 0, stream>>>(j);
-  else if (D == 64) quant_qkv_kernel<64><<<grid, 256, 0, stream>>>(j);
-  else quant_qkv_kernel<32><<<grid, 256, 0, stream>>>(j);
+  INTFA_D_SWITCH(D, (quant_qkv_kernel<DD><<<grid, 256, 0, stream>>>(j)))
   int rc = check_launch("quant_qkv");
   if (rc || !v) return rc;
   return v_quant_launch(v, v_st, workspace, j.chunks, v8, vs, mode, B, Hkv, Nk, D, stream);

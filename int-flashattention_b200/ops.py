@@ -27,7 +27,7 @@ def default_G(head_dim, variant="full"):
     flash_atten_full_int8.py:88).  half-int8: 128 -- its result does not depend on G beyond fp16
     rounding, and 128-wide KV tiles are the faster ones at both head sizes."""
     if variant == "half":
-        return 128
+        return 64 if head_dim == 256 else 128      # (fp16 V tiles of 128 keys x 256 channels do not fit next to K)
     return 128 if head_dim >= 128 else (64 if head_dim >= 64 else 32)
 
 

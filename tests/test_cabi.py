@@ -65,9 +65,12 @@ def test_version_and_error_text(lib):
 def test_validation_rejects_before_launch(lib):
     h = lib.load()
     P = lib.IntfaFwdParams()
-    P.B, P.H, P.Nq, P.Nk, P.D, P.G = 1, 1, 128, 128, 16, 64
-    assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_UNSUPPORTED       # head_dim 16
+    P.B, P.H, P.Nq, P.Nk, P.D, P.G = 1, 1, 128, 128, 48, 64
+    assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_UNSUPPORTED       # head_dim 48: not one of 16, 32, 64, 128, 256
     assert "head_dim" in lib.last_error()
+    P.D, P.G, P.variant = 256, 128, lib.VARIANT_HALF
+    assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_UNSUPPORTED       # half-int8 at head_dim 256: G = 64 only
+    P.variant = lib.VARIANT_FULL
     P.D = 128
     P.Nq = 100
     assert h.intfa_fwd(ctypes.byref(P), None) == lib.ERR_INVALID_ARG       # a ragged Nq is fine; q is NULL

@@ -391,10 +391,13 @@ def test_prologue_plus_forward(pkg, oracle, dev):
 
 
 def test_unsupported_shapes_raise(pkg, dev):
-    q = torch.zeros(1, 1, 128, 16, dtype=torch.int8, device=dev)
     s = torch.ones(1, 1, 128, device=dev)
-    with pytest.raises(pkg.IntfaError, match="head_dim"):
+    q = torch.zeros(1, 1, 128, 48, dtype=torch.int8, device=dev)
+    with pytest.raises(AssertionError):                      # the reference's own assertion (flash_atten_full_int8.py:193)
         pkg.attention_full_int8(q, q, q, s, s, torch.ones(1, 1, device=dev), False, 1.0)
+    q = torch.zeros(1, 1, 128, 256, dtype=torch.int8, device=dev)
+    with pytest.raises(pkg.IntfaError, match="G=64 only"):   # fp16 V tiles of 128 keys x 256 channels do not fit
+        pkg.attention_int8(q, q, q.half(), s, s, False, 1.0, G=128)
 
 
 # ------------------------------------------------------------------------------- full-size workloads
@@ -601,6 +604,98 @@ def test_head_dim_32(variant, G, N, causal, pkg, oracle, dev):
     _close(oracle, out, ref)
     g8, gs = pkg.quant_pertoken(q.to(dev))
     assert torch.equal(g8.cpu(), q8) and torch.equal(gs.cpu(), qs.float())
+
+
+@pytest.mark.parametrize("variant,G,N,causal", [("full", 32, 256, False), ("full", 32, 384, True), ("full", 64, 256, True),
+                                                ("full", 128, 512, False), ("half", 64, 256, True), ("half", 128, 384, False),
+                                                ("full", 32, 100, True), ("half", 128, 77, False)])
+def test_head_dim_16(variant, G, N, causal, pkg, oracle, dev):
+    """head_dim 16 (the smallest the reference's ops accept, flash_atten_full_int8.py:193): 16-byte rows, loaded into
+    the 32-wide tiles with the upper half zero-filled."""
+    B, H, D = 2, 3, 16
+    q, k, v = tuple(torch.randn(B, H, N, D, generator=torch.Generator().manual_seed(195 + i)).half() for i in range(3))
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    sm = D ** -0.5
+    if variant == "full":
+        v8, vs = oracle.quant_perchannel(v)
+        ref = oracle.attention_full_int8(q8, k8, v8, qs, ks, vs, causal, sm, G=G)
+        out = pkg.attention_full_int8(q8.to(dev), k8.to(dev), v8.to(dev), qs.to(dev), ks.to(dev), vs.to(dev), causal, sm, G=G)
+        g8, gs = pkg.quant_perchannel(v.to(dev))
+        assert torch.equal(g8.cpu(), v8) and torch.equal(gs.cpu(), vs.float())
+        t8, ts = pkg.quant_pertensor(v.to(dev))
+        r8, rs = oracle.quant_pertensor(v)
+        assert torch.equal(t8.cpu(), r8) and torch.equal(ts.cpu(), rs.float())
+    else:
+        ref = oracle.attention_int8(q8, k8, v, qs, ks, causal, sm, G=G)
+        out = pkg.attention_int8(q8.to(dev), k8.to(dev), v.to(dev), qs.to(dev), ks.to(dev), causal, sm, G=G)
+    pkg.check_status()
+    assert out.shape == (B, H, N, D)
+    _close(oracle, out, ref)
+    g8, gs = pkg.quant_pertoken(q.to(dev))
+    assert torch.equal(g8.cpu(), q8) and torch.equal(gs.cpu(), qs.float())
+    f = pkg.quant_qkv(q.to(dev), k.to(dev), v.to(dev), "per_channel")
+    assert torch.equal(f[0].cpu(), q8) and torch.equal(f[2].cpu(), k8)
+    assert torch.equal(f[4].cpu(), oracle.quant_perchannel(v)[0])
+
+
+@pytest.mark.parametrize("variant,G,N,causal", [("full", 128, 256, False), ("full", 128, 512, True), ("full", 64, 384, True),
+                                                ("full", 64, 256, False), ("half", 64, 256, True), ("half", 64, 384, False),
+                                                ("full", 128, 200, True), ("half", 64, 77, False), ("full", 64, 333, False)])
+def test_head_dim_256(variant, G, N, causal, pkg, oracle, dev):
+    """head_dim 256 (the largest the reference's ops accept): Q and K as two 128-byte panels, every query tile taken
+    twice by the same CTA -- once per half of the V channels."""
+    B, H, D = 2, 3, 256
+    q, k, v = tuple(torch.randn(B, H, N, D, generator=torch.Generator().manual_seed(295 + i)).half() for i in range(3))
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    sm = D ** -0.5
+    if variant == "full":
+        v8, vs = oracle.quant_perchannel(v)
+        ref = oracle.attention_full_int8(q8, k8, v8, qs, ks, vs, causal, sm, G=G)
+        out = pkg.attention_full_int8(q8.to(dev), k8.to(dev), v8.to(dev), qs.to(dev), ks.to(dev), vs.to(dev), causal, sm, G=G)
+        g8, gs = pkg.quant_perchannel(v.to(dev))
+        assert torch.equal(g8.cpu(), v8) and torch.equal(gs.cpu(), vs.float())
+    else:
+        ref = oracle.attention_int8(q8, k8, v, qs, ks, causal, sm, G=G)
+        out = pkg.attention_int8(q8.to(dev), k8.to(dev), v.to(dev), qs.to(dev), ks.to(dev), causal, sm, G=G)
+    pkg.check_status()
+    _close(oracle, out, ref)
+    g8, gs = pkg.quant_pertoken(q.to(dev))
+    assert torch.equal(g8.cpu(), q8) and torch.equal(gs.cpu(), qs.float())
+    f = pkg.quant_qkv(q.to(dev), k.to(dev), v.to(dev), "per_channel")
+    assert torch.equal(f[0].cpu(), q8) and torch.equal(f[2].cpu(), k8)
+    assert torch.equal(f[4].cpu(), oracle.quant_perchannel(v)[0])
+
+
+@pytest.mark.parametrize("variant,D,G", [("full", 256, 128), ("full", 256, 64), ("half", 256, 64), ("full", 16, 32), ("half", 16, 64)])
+def test_carried_state_at_head_dims_16_and_256(variant, D, G, pkg, oracle, dev):
+    """(m,l,acc) carried in place over KV chunks == one pass, bit for bit, also where a query tile is taken in two
+    passes that both read the carried m and l (head dim 256) and where the rows in memory are narrower than the
+    kernel's tiles (head dim 16)."""
+    B, H, N = 1, 2, 512
+    q, k, v = tuple(torch.randn(B, H, N, D, generator=torch.Generator().manual_seed(395 + i)).mul(0.5).half() for i in range(3))
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    v8, vs = oracle.quant_perchannel(v)
+    vv = (v8 if variant == "full" else v).to(dev)
+    q8d, k8d, qsd, ksd, vsd = q8.to(dev), k8.to(dev), qs.to(dev).float(), ks.to(dev).float(), vs.to(dev).float()
+    sm = D ** -0.5
+    fn = (lambda *a, **kw: pkg.attention_full_int8(a[0], a[1], a[2], a[3], a[4], vsd, True, sm, G=G, **kw)) \
+        if variant == "full" else (lambda *a, **kw: pkg.attention_int8(a[0], a[1], a[2], a[3], a[4], True, sm, G=G, **kw))
+    one, lse = fn(q8d, k8d, vv, qsd, ksd, return_lse=True)
+    st = None
+    for c in range(0, N, 256):
+        last = c + 256 >= N
+        res = fn(q8d, k8d[:, :, c:c + 256], vv[:, :, c:c + 256], qsd, ksd[:, :, c:c + 256].contiguous(),
+                 state=st, kv_offset=c, return_state=not last, write_o=last)
+        st = None if last else res[1]
+    pkg.check_status()
+    assert torch.equal(res, one)
+    ref, (m, l, _) = oracle.int8_attention(q8, k8, v8 if variant == "full" else v, qs, ks, vs, True, sm,
+                                           variant=variant, G=G, return_state=True)
+    _close(oracle, one, ref)
+    assert (lse.cpu() - oracle.log2_lse(m, l)).abs().max() < 1e-3
 
 
 def test_status_word_clean(pkg, dev):
