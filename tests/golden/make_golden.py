@@ -8,7 +8,7 @@ per case.  The reference's configs.py queries the GPU driver at import
 placed in sys.modules first; nothing else of the reference is replaced.
 
 Usage (only where a checkout of the reference is present; the fixtures are committed):
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [case name ...]
 """
 import importlib
 import os
@@ -78,12 +78,19 @@ CASES = [
     ("full_c_shipped_d64", "full", True, 1, 1, 256, 64, 128, 64, 0.125, "normal_half", False),
     ("acc_test_full_d32", "full", False, 1, 1, 32, 32, 32, 32, 1.0, "uniform", False),
     ("acc_test_half_d32", "half", False, 1, 1, 32, 32, 32, 32, 1.0, "uniform", False),
+    # the largest head dim the ops accept (flash_atten_full_int8.py:193).  (The smallest, 16, passes the host
+    # assertion but no kernel can be built for it: every BLOCK_N of configs.py:16 is >= 32 and
+    # flash_atten_full_int8.py:88 / flash_atten_int8.py:82 assert BLOCK_N <= HEAD_DIM.)
+    ("full_nc_d256_g128", "full", False, 1, 1, 256, 256, 128, 128, 0.0625, "normal", False),
+    ("half_c_d256_g64", "half", True, 1, 1, 256, 256, 128, 64, 0.0625, "normal", True),
 ]
 
 
-def main(ref_dir):
+def main(ref_dir, only=()):
     quant_pertoken, quant_pertensor = load_quantisers(ref_dir)
     for i, (name, variant, causal, B, H, N, D, BM, BN, sm_scale, dist, outlier) in enumerate(CASES):
+        if only and name not in only:
+            continue
         full, half = load_reference(ref_dir, BM, BN)
         q, k, v = make_inputs(1000 + i, B, H, N, D, dist, outlier)
         q8, qs = quant_pertoken(q)
@@ -104,6 +111,6 @@ def main(ref_dir):
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        sys.exit("usage: make_golden.py <path to the reference checkout>")
-    main(sys.argv[1])
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <path to the reference checkout> [case name ...]")
+    main(sys.argv[1], tuple(sys.argv[2:]))
