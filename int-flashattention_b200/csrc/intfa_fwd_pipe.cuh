@@ -28,11 +28,9 @@ constexpr int kPipeThreads = 512;
 constexpr int kPipeSoftmaxThreads = 256;
 constexpr int kPipeCorrThreads = 128;
 // Registers: the CTA is launched with kPipeLaunchRegs per thread and setmaxnreg only moves registers around
-// INSIDE that allocation -- an increase beyond it would block for ever, hence the static_assert.
+// INSIDE that allocation -- an increase beyond it would block for ever, hence the static_assert in PipeCfg.
 constexpr int kPipeLaunchRegs = (65536 / kPipeThreads) / 8 * 8;
-constexpr int kPipeServiceRegs = 40, kPipeSoftmaxRegs = 136, kPipeCorrRegs = 184;
-static_assert(128 * kPipeServiceRegs + kPipeSoftmaxThreads * kPipeSoftmaxRegs + kPipeCorrThreads * kPipeCorrRegs <=
-                  kPipeThreads * kPipeLaunchRegs, "setmaxnreg budget exceeds the registers the CTA is launched with");
+constexpr int kPipeServiceRegs = 40;
 
 // D: channels of V and of the accumulator that one pass covers (and the width the tensor-core tiles are built for);
 // DQ: head dim of Q and K.  DQ == D except at head dim 256, which runs as DQ = 256, D = 128: every query tile is
@@ -60,6 +58,13 @@ struct PipeCfg {
   // twice.  Where the head is wider than the step (head_dim 128 at G = 64) the accumulator warps are the busier
   // side and the softmax groups keep l, handing it over like the running max (measured: 582 against 474 TOPS).
   static constexpr bool L_IN_ACC = G >= D;
+  // setmaxnreg split between the softmax and the accumulator warps.  The accumulator row of 128 channels fits either
+  // way; at the headline shape the softmax passes gain more from 16 further registers than the update loses
+  // (measured +2 %), at the other shapes it is the other way round.
+  static constexpr int SOFTMAX_REGS = (FULL && D == 128 && G == 128) ? 152 : 136;
+  static constexpr int CORR_REGS = (FULL && D == 128 && G == 128) ? 168 : 184;
+  static_assert(128 * kPipeServiceRegs + kPipeSoftmaxThreads * SOFTMAX_REGS + kPipeCorrThreads * CORR_REGS <=
+                    kPipeThreads * kPipeLaunchRegs, "setmaxnreg budget exceeds the registers the CTA is launched with");
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
   static constexpr int OFF_V = OFF_K + NSK * K_BYTES;
@@ -393,10 +398,10 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
     __syncwarp();
   } else if (warp >= 4 && warp < 12) {
-    reg_alloc<kPipeSoftmaxRegs>();
+    reg_alloc<C::SOFTMAX_REGS>();
 #include "intfa_fwd_pipe_softmax.inc"
   } else if (warp >= 12) {
-    if constexpr (kPipeCorrRegs > kPipeLaunchRegs) reg_alloc<kPipeCorrRegs>(); else reg_dealloc<kPipeCorrRegs>();
+    if constexpr (C::CORR_REGS > kPipeLaunchRegs) reg_alloc<C::CORR_REGS>(); else reg_dealloc<C::CORR_REGS>();
 #include "intfa_fwd_pipe_update.inc"
   }
 
