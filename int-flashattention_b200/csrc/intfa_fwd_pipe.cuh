@@ -59,10 +59,14 @@ struct PipeCfg {
   // side and the softmax groups keep l, handing it over like the running max (measured: 582 against 474 TOPS).
   static constexpr bool L_IN_ACC = G >= D;
   // setmaxnreg split between the softmax and the accumulator warps.  The accumulator row of 128 channels fits either
-  // way; at the headline shape the softmax passes gain more from 16 further registers than the update loses
-  // (measured +2 %), at the other shapes it is the other way round.
-  static constexpr int SOFTMAX_REGS = (FULL && D == 128 && G == 128) ? 152 : 136;
-  static constexpr int CORR_REGS = (FULL && D == 128 && G == 128) ? 168 : 184;
+  // way; with 128-column KV steps, and for half-int8 (no accumulator row in registers), the softmax passes gain more
+  // from 16 further registers than the update loses (measured +2..3 %); full-int8 at G = 64 is the other way round.
+  // instructions of never-executed filler between the softmax passes (see intfa_fwd_pipe_softmax.inc): 2 KB for every
+  // configuration but full-int8 at head dim 64, which measured best without
+  static constexpr int CODE_FILLER = (FULL && D == 64) ? 0 : 128;
+  static constexpr bool MORE_SOFTMAX_REGS = !FULL || G == 128;
+  static constexpr int SOFTMAX_REGS = MORE_SOFTMAX_REGS ? 152 : 136;
+  static constexpr int CORR_REGS = MORE_SOFTMAX_REGS ? 168 : 184;
   static_assert(128 * kPipeServiceRegs + kPipeSoftmaxThreads * SOFTMAX_REGS + kPipeCorrThreads * CORR_REGS <=
                     kPipeThreads * kPipeLaunchRegs, "setmaxnreg budget exceeds the registers the CTA is launched with");
   static constexpr int OFF_Q = 0;

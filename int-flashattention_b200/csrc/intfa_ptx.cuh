@@ -101,6 +101,14 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, code));
 }
 
+// N instructions (16 bytes each) that do nothing: filler to move the code behind it in the instruction cache.
+// Placed on a path that is never taken.
+template <int N>
+__device__ __forceinline__ void code_filler() {
+#pragma unroll
+  for (int i = 0; i < N; ++i) asm volatile("nanosleep.u32 0;");
+}
+
 // generic-proxy writes (st.shared) -> visible to the async proxy (TMA / tcgen05.mma operand reads)
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
