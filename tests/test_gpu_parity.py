@@ -435,6 +435,12 @@ def test_full_size_full_int8_noncausal(pkg, oracle, dev):
     _full_size(pkg, oracle, dev, 4, 32, 8192, 128, "full", False, 1001, False, [(0, 0), (3, 31)])
 
 
+def test_long_rows_at_head_dim_256(pkg, oracle, dev):
+    """Head dim 256 on 4096-token rows (32 KV steps, two passes per query tile, causal): sampled slices against the
+    oracle, run-to-run and batch-permutation equality."""
+    _full_size(pkg, oracle, dev, 2, 8, 4096, 256, "full", True, 1005, False, [(0, 0), (1, 7)])
+
+
 def test_full_size_half_int8_causal(pkg, oracle, dev):
     """The half-int8 workload at full size: batch 8, heads 32, seq 4096, head_dim 128, causal, outlier channel."""
     _full_size(pkg, oracle, dev, 8, 32, 4096, 128, "half", True, 1002, True, [(0, 0), (7, 13)])
