@@ -30,6 +30,7 @@ extern "C" {
 
 #define INTFA_VARIANT_FULL 0         /* int8 Q/K/V, int8 P  (flash_atten_full_int8.py) */
 #define INTFA_VARIANT_HALF 1         /* int8 Q/K, fp16 V, fp16 P (flash_atten_int8.py)  */
+#define INTFA_VARIANT_HALF_FP8 2     /* int8 Q/K, float8_e5m2 V and P (flash_atten_int8.py:55-56); v is one byte per element */
 
 #define INTFA_OUT_FP16 0             /* o as fp16: the Triton ops (flash_atten_full_int8.py:194-195) */
 #define INTFA_OUT_BF16 1             /* o as bf16: csrc/flash_fwd_hdim128_bf16_sm80_{full,half}_qi8.cu */

@@ -10,7 +10,7 @@ LIB_PATH = os.path.join(_PKG_DIR, "libintfa.so")
 
 OK = 0
 ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_WAIT, ERR_TOO_LARGE = -1, -2, -3, -4, -5
-VARIANT_FULL, VARIANT_HALF = 0, 1
+VARIANT_FULL, VARIANT_HALF, VARIANT_HALF_FP8 = 0, 1, 2
 VSCALE_PER_TENSOR, VSCALE_PER_CHANNEL = 0, 1
 
 EXPORTS = ("intfa_version", "intfa_last_error", "intfa_fwd", "intfa_quant_pertoken",

@@ -68,8 +68,8 @@ int intfa_sm_count(void) { return sm_count_cached(); }
 
 int intfa_fwd(const IntfaFwdParams* p, void* stream) {
   if (!p) return set_error(INTFA_ERR_INVALID_ARG, "params is NULL");
-  if (p->variant != INTFA_VARIANT_FULL && p->variant != INTFA_VARIANT_HALF)
-    return set_error(INTFA_ERR_INVALID_ARG, "variant must be INTFA_VARIANT_FULL or INTFA_VARIANT_HALF");
+  if (p->variant != INTFA_VARIANT_FULL && p->variant != INTFA_VARIANT_HALF && p->variant != INTFA_VARIANT_HALF_FP8)
+    return set_error(INTFA_ERR_INVALID_ARG, "variant must be INTFA_VARIANT_FULL, INTFA_VARIANT_HALF or INTFA_VARIANT_HALF_FP8");
   const bool full = p->variant == INTFA_VARIANT_FULL;
   if (p->B <= 0 || p->H <= 0 || p->Nq <= 0 || p->Nk <= 0)
     return set_error(INTFA_ERR_INVALID_ARG, "B, H, Nq, Nk must be positive");
@@ -88,7 +88,7 @@ int intfa_fwd(const IntfaFwdParams* p, void* stream) {
   int rc;
   if ((rc = check_tma_tensor("q", p->q, p->q_stride, 1))) return rc;
   if ((rc = check_tma_tensor("k", p->k, p->k_stride, 1))) return rc;
-  if ((rc = check_tma_tensor("v", p->v, p->v_stride, full ? 1 : 2))) return rc;
+  if ((rc = check_tma_tensor("v", p->v, p->v_stride, p->variant == INTFA_VARIANT_HALF ? 2 : 1))) return rc;
   if (!p->q_scale || !p->k_scale) return set_error(INTFA_ERR_INVALID_ARG, "q_scale / k_scale is NULL");
   if (!aligned16(p->k_scale) || p->ks_stride[0] % 4 != 0 || p->ks_stride[1] % 4 != 0)
     return set_error(INTFA_ERR_INVALID_ARG, "k_scale must be 16-byte aligned with (B,H) strides that are multiples of 4");

@@ -172,9 +172,9 @@ static constexpr CUtensorMapSwizzle swizzle_of_row_bytes(int bytes) {
 
 // One CTA per SM.  The tensor maps describe the tensors with their own head dim (a->D); the boxes are as wide as the
 // kernel's tiles, so at head dim 16 the upper half of every 32-wide box lies outside the tensor and arrives as zeros.
-template <int D, int G, bool FULL, bool PRNE, bool RAGGED, int DQ = D>
+template <int D, int G, bool FULL, bool PRNE, bool RAGGED, int DQ = D, bool F8V = false>
 static int launch_pipe(const IntfaFwdParams* a, const KParams& kp, cudaStream_t stream) {
-  using C = PipeCfg<D, G, FULL, DQ>;
+  using C = PipeCfg<D, G, FULL, DQ, F8V>;
   static_assert(C::SMEM_BYTES <= 227 * 1024, "shared memory");
   CUtensorMap tmQ, tmK, tmV;
   const CUtensorMapSwizzle swzQK = swizzle_of_row_bytes(C::QK_ROWB), swzV = swizzle_of_row_bytes(C::V_ROWB);
@@ -182,12 +182,12 @@ static int launch_pipe(const IntfaFwdParams* a, const KParams& kp, cudaStream_t 
   int rc;
   if ((rc = make_tmap(&tmQ, a->q, 1, a->q_stride, a->B, a->H, a->Nq, hd, C::QK_ROWB, kBM, swzQK))) return rc;
   if ((rc = make_tmap(&tmK, a->k, 1, a->k_stride, a->B, kv_heads(a), a->Nk, hd, C::QK_ROWB, G, swzQK))) return rc;
-  if constexpr (FULL) {
+  if constexpr (C::BYTE_PV) {
     if ((rc = make_tmap(&tmV, a->v, 1, a->v_stride, a->B, kv_heads(a), a->Nk, hd, D, G, swzV))) return rc;
   } else {
     if ((rc = make_tmap(&tmV, a->v, 2, a->v_stride, a->B, kv_heads(a), a->Nk, hd, D >= 64 ? 64 : D, G, swzV))) return rc;
   }
-  auto kern = intfa_fwd_pipe_kernel<D, G, FULL, PRNE, RAGGED, DQ>;
+  auto kern = intfa_fwd_pipe_kernel<D, G, FULL, PRNE, RAGGED, DQ, F8V>;
   static std::atomic<bool> attr_done[64];     // per instantiation and device (the attribute is per device)
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return set_error(INTFA_ERR_CUDA, "cannot query the current device");
@@ -234,6 +234,7 @@ int fwd_dispatch(const IntfaFwdParams* a, cudaStream_t stream) {
   kp.MB = (a->Nq + kBM - 1) / kBM;            // the last query tile may be partial (pipelined kernel only)
   kp.num_tiles = (int)((long long)a->B * a->H * kp.MB);   // fits: intfa_fwd() has checked it
   const bool full = a->variant == INTFA_VARIANT_FULL;
+  const bool f8v = a->variant == INTFA_VARIANT_HALF_FP8;
   const bool rne = full && a->p_round == 1;
   const int D = a->D, G = a->G;
   // Sequence lengths that are not multiples of the tile sizes run the instantiation that masks the last tiles
@@ -247,6 +248,8 @@ int fwd_dispatch(const IntfaFwdParams* a, cudaStream_t stream) {
     if (full) return rne ? launch_pipe<DD, GG, true, true, false, DQ>(a, kp, stream)                     \
                          : launch_pipe<DD, GG, true, false, false, DQ>(a, kp, stream);                   \
     if constexpr (HALF) {                                                                                \
+      if (f8v) return ragged ? launch_pipe<DD, GG, false, false, true, DQ, true>(a, kp, stream)          \
+                             : launch_pipe<DD, GG, false, false, false, DQ, true>(a, kp, stream);        \
       return ragged ? launch_pipe<DD, GG, false, false, true, DQ>(a, kp, stream)                         \
                     : launch_pipe<DD, GG, false, false, false, DQ>(a, kp, stream);                       \
     }                                                                                                    \

@@ -36,20 +36,24 @@ constexpr int kPipeServiceRegs = 40;
 // DQ: head dim of Q and K.  DQ == D except at head dim 256, which runs as DQ = 256, D = 128: every query tile is
 // taken twice in a row by the same CTA, once per half of the V channels (the accumulator row of one thread and the
 // TMEM columns hold 128 channels); S, the running max and P are the same in both passes.
-template <int D, int G, bool FULL, int DQ = D>
+// F8V: the half-int8 op with V (and therefore P) in float8_e5m2 (flash_atten_int8.py:55-56): one-byte P and V tiles laid
+// out like the int8 ones, P V with kind::f8f6f4 accumulating in fp32 like the fp16 form.
+template <int D, int G, bool FULL, int DQ = D, bool F8V = false>
 struct PipeCfg {
+  static_assert(!(FULL && F8V), "fp8 V belongs to the half-int8 op");
+  static constexpr bool BYTE_PV = FULL || F8V;                     // P and V elements are one byte
   static_assert(DQ == D || (DQ == 256 && D == 128), "head dims");
   static constexpr int NVH = DQ / D;                               // passes per query tile
   static constexpr int QK_ROWB = DQ < 128 ? DQ : 128;              // Q and K sit in shared memory as panels of [rows][QK_ROWB bytes]
   static constexpr int QK_PANELS = DQ / QK_ROWB;
   static constexpr int Q_BYTES = kBM * DQ;
   static constexpr int K_BYTES = G * DQ;
-  static constexpr int V_BYTES = FULL ? G * D : G * D * 2;         // int8, or fp16 as D/64 boxes of [G keys][64 channels]
-  static constexpr int P_BYTES = FULL ? kBM * G : kBM * G * 2;     // int8, or fp16 as G/64 blocks of [128 rows][64 columns]
+  static constexpr int V_BYTES = BYTE_PV ? G * D : G * D * 2;         // int8, or fp16 as D/64 boxes of [G keys][64 channels]
+  static constexpr int P_BYTES = BYTE_PV ? kBM * G : kBM * G * 2;     // int8, or fp16 as G/64 blocks of [128 rows][64 columns]
   static constexpr int KS_BYTES = G * 4;
   static constexpr bool BIG = DQ > 128 && G == 128;                // 32 KB K tiles: three stages are what fits
   static constexpr int NSK = BIG ? 3 : 4;                          // K stages
-  static constexpr int NSV = BIG ? 3 : (FULL || G == 64) ? 4 : 2;  // V stages (fp16 V tiles are twice the size)
+  static constexpr int NSV = BIG ? 3 : (BYTE_PV || G == 64) ? 4 : 2;  // V stages (fp16 V tiles are twice the size)
   static constexpr int NKS = 8;                                    // K-scale slots: a slot is rewritten 8 steps later, when
                                                                    // the three S buffers have long forced its step out
   static constexpr int NSB = 3;                                    // S buffers in TMEM
@@ -96,15 +100,17 @@ struct PipeCfg {
   static constexpr uint32_t SBO_QK = 8 * QK_ROWB;
   // start-address offset (16-byte units) of the kk-th 32-byte K slice of a [ROWS][DQ] operand
   __host__ __device__ static constexpr uint32_t qk_slice(int kk, int rows) { return (uint32_t)((kk / 4) * ((rows * QK_ROWB) >> 4) + 2 * (kk % 4)); }
-  static constexpr uint64_t SWZ_P = FULL ? ((G == 128) ? kSwz128 : (G == 64) ? kSwz64 : kSwz32) : kSwz128;
-  static constexpr uint32_t SBO_P = FULL ? 8 * G : 1024;
+  static constexpr uint64_t SWZ_P = BYTE_PV ? ((G == 128) ? kSwz128 : (G == 64) ? kSwz64 : kSwz32) : kSwz128;
+  static constexpr uint32_t SBO_P = BYTE_PV ? 8 * G : 1024;
   // V rows: D bytes (int8), or boxes of min(D, 64) fp16 channels = 128 / 64 bytes
-  static constexpr int V_BOXES = FULL ? 1 : (D >= 64 ? D / 64 : 1);
-  static constexpr int V_ROWB = FULL ? D : (D >= 64 ? 128 : 2 * D);
+  static constexpr int V_BOXES = BYTE_PV ? 1 : (D >= 64 ? D / 64 : 1);
+  static constexpr int V_ROWB = BYTE_PV ? D : (D >= 64 ? 128 : 2 * D);
   static constexpr uint64_t SWZ_V = (V_ROWB == 128) ? kSwz128 : (V_ROWB == 64) ? kSwz64 : kSwz32;
   static constexpr uint32_t SBO_V = 8 * V_ROWB;
   static constexpr uint32_t IDESC_QK = make_idesc(2, 1, 1, 0, 0, kBM, G);
-  static constexpr uint32_t IDESC_PV = FULL ? make_idesc(2, 1, 1, 0, 1, kBM, D) : make_idesc(1, 0, 0, 0, 1, kBM, D);
+  // (kind::f8f6f4: A / B format 1 = e5m2, D format 1 = f32)
+  static constexpr uint32_t IDESC_PV = FULL ? make_idesc(2, 1, 1, 0, 1, kBM, D)
+                                       : F8V ? make_idesc(1, 1, 1, 0, 1, kBM, D) : make_idesc(1, 0, 0, 0, 1, kBM, D);
   // fp16 x fp16 -> fp32, K = 16: writes the fp32 constant 1.5*2^23 into a whole accumulator tile
   static constexpr uint32_t IDESC_ARM_S = make_idesc(1, 0, 0, 0, 0, kBM, G);
   static constexpr uint32_t IDESC_ARM_O = make_idesc(1, 0, 0, 0, 0, kBM, D);
@@ -115,11 +121,11 @@ enum PipeWait { PW_TILE = 32, PW_QE, PW_KE, PW_VE, PW_QF, PW_KF, PW_VF, PW_SFREE
 
 // RAGGED: Nq / Nk are not multiples of 128 / G -- the last query tile and the last KV step are partial.  A separate
 // instantiation, so that the code of the common case stays as small as it was (instruction cache).
-template <int D, int G, bool FULL, bool PRNE, bool RAGGED, int DQ = D>
+template <int D, int G, bool FULL, bool PRNE, bool RAGGED, int DQ = D, bool F8V = false>
 __global__ void __launch_bounds__(kPipeThreads, 1)
 intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const KParams p) {
-  using C = PipeCfg<D, G, FULL, DQ>;
+  using C = PipeCfg<D, G, FULL, DQ, F8V>;
   constexpr int NSK = C::NSK, NSV = C::NSV, NSB = C::NSB, NVH = C::NVH;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -288,7 +294,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           ok = mbar_wait(BAR(B_VEMPTY + sv), phv ^ 1, abort_flag, p.status, code_hi | PW_VE);
           if (!ok) break;
           mbar_expect_tx(BAR(B_VFULL + sv), C::V_BYTES);
-          if constexpr (FULL) {
+          if constexpr (C::BYTE_PV) {
             tma_load_4d(sV + sv * C::V_BYTES, &tmV, BAR(B_VFULL + sv), t.vh * D, jb * G, t.hk, t.b);
           } else {
 #pragma unroll
@@ -356,7 +362,7 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       uint32_t kv_it = 0, tseq = 0;
       bool ok = true;
       const uint64_t descP0 = make_smem_desc(sP, 16, C::SBO_P, C::SWZ_P);
-      const uint64_t descV0 = make_smem_desc(sV, FULL ? 16 : G * 128, C::SBO_V, C::SWZ_V);
+      const uint64_t descV0 = make_smem_desc(sV, C::BYTE_PV ? 16 : G * 128, C::SBO_V, C::SWZ_V);
       while (ok) {
         const int tile = next_tile(tseq, lane == 0, true);
         if (tile < 0) break;
@@ -383,6 +389,11 @@ intfa_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
               umma_f16(tO, descArm, descArm, C::IDESC_ARM_O, 0);
 #pragma unroll
               for (int kk = 0; kk < G / 32; ++kk) umma_i8(tO, ad0 + 2 * kk, vd0 + kk * ((32 * D) >> 4), C::IDESC_PV, 1);
+            } else if constexpr (F8V) {
+              // e5m2 P x e5m2 V (both one byte, laid out like the int8 tiles), fp32 accumulate straight into the accumulator
+              const uint32_t keep = (j > 0 || p.state_in) ? 1u : 0u;
+#pragma unroll
+              for (int kk = 0; kk < G / 32; ++kk) umma_f8(tA, ad0 + 2 * kk, vd0 + kk * ((32 * D) >> 4), C::IDESC_PV, kk > 0 ? 1u : keep);
             } else {
               // fp16 P (K-major, 64-column blocks of 128-byte rows) x fp16 V (MN-major), fp32 accumulate straight
               // into the accumulator; the first P V of a fresh work item overwrites it

@@ -101,8 +101,9 @@ def _fwd(variant, q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, *, G=Non
         raise TypeError("q and k must be int8")
     if full and v.dtype != torch.int8:
         raise TypeError("full-int8: v must be int8")
-    if not full and v.dtype != torch.float16:
-        raise TypeError("half-int8: v must be float16")
+    f8v = not full and v.dtype == torch.float8_e5m2       # V (and with it P) in fp8: flash_atten_int8.py:55-56
+    if not full and not f8v and v.dtype != torch.float16:
+        raise TypeError("half-int8: v must be float16 or float8_e5m2")
     B, H, Nq, D = q.shape
     Nk = k.shape[2]
     H_kv = k.shape[1]                          # grouped-query attention: fewer K/V heads than query heads
@@ -152,7 +153,7 @@ def _fwd(variant, q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, *, G=Non
     P.B, P.H, P.Nq, P.Nk, P.D = B, H, Nq, Nk, D
     P.H_kv = H_kv
     P.o_dtype = 1 if out_dtype == torch.bfloat16 else 0
-    P.variant = _lib.VARIANT_FULL if full else _lib.VARIANT_HALF
+    P.variant = _lib.VARIANT_FULL if full else (_lib.VARIANT_HALF_FP8 if f8v else _lib.VARIANT_HALF)
     P.causal = 1 if causal else 0
     P.sm_scale = float(sm_scale)
     P.G = int(G)
@@ -181,7 +182,7 @@ def _fwd(variant, q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, *, G=Non
     if debug_tap is not None:
         tile, step = debug_tap
         dbg_s = torch.zeros((128, G), dtype=torch.int32, device=q.device)
-        dbg_p = torch.zeros((128, G), dtype=torch.int8 if full else torch.float16, device=q.device)
+        dbg_p = torch.zeros((128, G), dtype=torch.int8 if full else (torch.uint8 if f8v else torch.float16), device=q.device)
         P.dbg_s, P.dbg_p, P.dbg_tile, P.dbg_step = dbg_s.data_ptr(), dbg_p.data_ptr(), int(tile), int(step)
         dbg = (dbg_s, dbg_p)
     if debug_wait is not None:                 # test hooks of the bounded waits: (limit in kilo-cycles, K step to leave out)
@@ -216,7 +217,8 @@ def attention_full_int8(q, k, v, q_scale, k_scale, v_scale, causal, sm_scale, **
 
 def attention_int8(q, k, v, q_scale, k_scale, causal, sm_scale, **kw):
     """Half-int8 attention forward (int8 Q/K, fp16 V and P).  Mirrors attention_int8 of
-    flash_atten_int8.py:181,217."""
+    flash_atten_int8.py:181,217.  V may also be torch.float8_e5m2: P is then cast to e5m2 as well and P V runs as an
+    fp8 matrix product with fp32 accumulation (flash_atten_int8.py:55-56,160)."""
     return _fwd("half", q, k, v, q_scale, k_scale, None, causal, sm_scale, **kw)
 
 

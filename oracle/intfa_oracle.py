@@ -100,7 +100,7 @@ def int8_attention(q8, k8, v, q_scale, k_scale, v_scale, causal, sm_scale, *,
                    state=None, q_offset=0, kv_offset=0, return_state=False):
     """Blockwise restatement of _attn_fwd_full_int8 / _attn_fwd_int8.
 
-    q8,k8 int8 [B,H,Nq|Nk,d]; v int8 (variant "full") or fp16 ("half") [B,H,Nk,d];
+    q8,k8 int8 [B,H,Nq|Nk,d]; v int8 (variant "full") or fp16 / float8_e5m2 ("half") [B,H,Nk,d];
     q_scale [B,H,Nq], k_scale [B,H,Nk] any float dtype (promoted to fp32 like
     flash_atten_full_int8.py:37-38); v_scale [B,H] or [B,H,d] (full only).
     KV is visited in groups of G columns (G = the reference's BLOCK_N), ascending like the Triton ops or, with
@@ -182,8 +182,11 @@ def int8_attention(q8, k8, v, q_scale, k_scale, v_scale, causal, sm_scale, *,
             tmp = tmp * vs_j / 127                                         # :61
             acc_new = acc_new + tmp                                        # :62
         else:
-            p16 = p.to(torch.float16)                                      # flash_atten_int8.py:58
-            acc_new = acc_new + torch.matmul(p16.float(), vj.float())      # :59
+            if vj.dtype == torch.float8_e5m2:
+                pq = p.to(torch.float8_e5m2)                               # flash_atten_int8.py:55-56 (V in fp8: P in fp8 too)
+            else:
+                pq = p.to(torch.float16)                                   # flash_atten_int8.py:58
+            acc_new = acc_new + torch.matmul(pq.float(), vj.float())       # :59
         return m_new, l_new, acc_new
 
     groups = list(range(0, Nk, G))

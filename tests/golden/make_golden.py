@@ -83,6 +83,10 @@ CASES = [
     # flash_atten_full_int8.py:88 / flash_atten_int8.py:82 assert BLOCK_N <= HEAD_DIM.)
     ("full_nc_d256_g128", "full", False, 1, 1, 256, 256, 128, 128, 0.0625, "normal", False),
     ("half_c_d256_g64", "half", True, 1, 1, 256, 256, 128, 64, 0.0625, "normal", True),
+    # (The half-int8 op with V in float8_e5m2, flash_atten_int8.py:55-56,160, runs under the interpreter too, but its
+    # emulation of the fp32 -> fp8 cast is not the GPU's: it adds the cut-off bit without carrying a mantissa overflow
+    # into the exponent (triton/runtime/interpreter.py, _convert_float), so such outputs would pin the emulator, not
+    # the reference.  No fixture is made for that branch.)
 ]
 
 

@@ -704,6 +704,27 @@ def test_carried_state_at_head_dims_16_and_256(variant, D, G, pkg, oracle, dev):
     assert (lse.cpu() - oracle.log2_lse(m, l)).abs().max() < 1e-3
 
 
+@pytest.mark.parametrize("B,H,N,D,G,causal", [(1, 2, 256, 128, 128, False), (2, 3, 384, 128, 64, True), (1, 4, 512, 64, 64, True),
+                                              (1, 2, 256, 64, 128, False), (2, 2, 300, 128, 128, True), (1, 2, 256, 32, 64, False),
+                                              (1, 2, 256, 256, 64, True), (1, 3, 200, 16, 64, False)])
+def test_half_int8_with_fp8_v(B, H, N, D, G, causal, pkg, oracle, dev):
+    """attention_int8 with V in float8_e5m2 (flash_atten_int8.py:55-56,160): P is cast to e5m2 too and P V is an fp8
+    product accumulated in fp32.  Against the oracle's restatement (torch's round-to-nearest-even fp8 cast)."""
+    g = torch.Generator().manual_seed(500 + N + D)
+    q, k, v = (torch.randn(B, H, N, D, generator=g).half() for _ in range(3))
+    q8, qs = oracle.quant_pertoken(q)
+    k8, ks = oracle.quant_pertoken(k)
+    vf = v.to(torch.float8_e5m2)
+    sm = D ** -0.5
+    ref = oracle.attention_int8(q8, k8, vf, qs, ks, causal, sm, G=G)
+    out = pkg.attention_int8(q8.to(dev), k8.to(dev), vf.to(dev), qs.to(dev), ks.to(dev), causal, sm, G=G)
+    pkg.check_status()
+    _close(oracle, out, ref)
+    # and it is not the fp16 result: fp8 P and V cost two to three decimal digits
+    o16 = pkg.attention_int8(q8.to(dev), k8.to(dev), v.to(dev), qs.to(dev), ks.to(dev), causal, sm, G=G)
+    assert float((out.float() - o16.float()).abs().max()) > 1e-3
+
+
 def test_status_word_clean(pkg, dev):
     assert pkg.check_status(dev) == 0
 
