@@ -34,6 +34,11 @@ WORKLOADS = {
     "c3_half_b8_h32_n4096_d128_causal": ("half", 8, 32, 4096, 128, True, 1.0, True),
     "c4shard_full_b8_h64_n4096_d128": ("full", 8, 64, 4096, 128, False, 1.0, False),
     "c1_full_b1_h4_n512_d64": ("full", 1, 4, 512, 64, False, 1.0, False),
+    # the other head dims of the reference's sweep (benchmark.py:23 runs d=64; the ops accept 16 to 256)
+    "d64_full_b4_h32_n8192": ("full", 4, 32, 8192, 64, False, 1.0, False),
+    "d64_half_b4_h32_n8192_causal": ("half", 4, 32, 8192, 64, True, 1.0, True),
+    "d256_full_b4_h16_n8192": ("full", 4, 16, 8192, 256, False, 1.0, False),
+    "d256_half_b4_h16_n8192_causal": ("half", 4, 16, 8192, 256, True, 1.0, True),
     # long-context causal ring over all ranks (sequence-parallel; needs --gpus >= 2): N is the GLOBAL sequence
     "c5_ring_full_b1_h32_n131072_d128_causal": ("full", 1, 32, 131072, 128, True, 0.5, False),
     # small cases of the same kernels for profiler captures (a few hundred MB on the device)
