@@ -65,9 +65,13 @@ struct PipeCfg {
   // setmaxnreg split between the softmax and the accumulator warps.  The accumulator row of 128 channels fits either
   // way; with 128-column KV steps, and for half-int8 (no accumulator row in registers), the softmax passes gain more
   // from 16 further registers than the update loses (measured +2..3 %); full-int8 at G = 64 is the other way round.
-  // instructions of never-executed filler between the softmax passes (see intfa_fwd_pipe_softmax.inc): 2 KB for every
-  // configuration but full-int8 at head dim 64, which measured best without
-  static constexpr int CODE_FILLER = (FULL && D == 64) ? 0 : 128;
+  // A vectorised pass A for the causal diagonal band (otherwise those steps take the general, scalar path): compiled in
+  // for 128-column KV steps, where it measured +2..5 % on causal workloads; with 64-column steps its code costs the
+  // non-causal case more (instruction cache) than it gives.
+  static constexpr bool BAND_FAST = G == 128;
+  // instructions of never-executed filler between the softmax passes (see intfa_fwd_pipe_softmax.inc): 4 KB with the
+  // band path compiled in, else 2 KB, and none for full-int8 at head dim 64 -- each the best of a sweep
+  static constexpr int CODE_FILLER = BAND_FAST ? 256 : (FULL && D == 64) ? 0 : 128;
   static constexpr bool MORE_SOFTMAX_REGS = !FULL || G == 128;
   static constexpr int SOFTMAX_REGS = MORE_SOFTMAX_REGS ? 152 : 136;
   static constexpr int CORR_REGS = MORE_SOFTMAX_REGS ? 168 : 184;
